@@ -9,7 +9,9 @@ slot, whose index addresses the storage of all state groups (a model without
 stateful mixers still gets slots: the engine keeps per-request sampling state
 there).  Pages and the slot are given back when a request ends or is
 preempted; pages of a windowed group are given back as soon as the window has
-passed them; what is given back is used again.
+passed them (those of the first tokens that a window keeps stay), pages of a
+group whose queries see their own chunk of positions only as soon as the chunk
+has ended; what is given back is used again.
 
 Like the reference's ``KVCacheManager`` (crates/rllm-cache/src/manager.rs:34-269)
 allocation is all-or-nothing (:132-166), block tables only grow (:162-163),
@@ -88,12 +90,14 @@ class CacheManager:
         kinds = (c_int * max(G, 1))(*[0 if g in self.paged else 1 for g in range(G)])
         windows = (c_int * max(G, 1))(*[(-1 if getattr(n, "window", None) is None else int(n.window))
                                         for n in self.needs])
+        keeps = (c_int * max(G, 1))(*[int(getattr(n, "keep_first", 0) or 0) for n in self.needs])
+        chunks = (c_int * max(G, 1))(*[int(getattr(n, "chunk", None) or 0) for n in self.needs])
         per_group = [0] * G
         for g, c in zip(self.paged, counts):
             if c < 1:
                 raise ValueError("a pool needs at least one page")
             per_group[g] = int(c)
-        h = core().rllm_cache_new(c_int(G), kinds, windows, (c_int * max(G, 1))(*per_group), c_int(page_size),
+        h = core().rllm_cache_new(c_int(G), kinds, windows, keeps, chunks, (c_int * max(G, 1))(*per_group), c_int(page_size),
                                   c_int(max_seqs), c_int(1 if enable_prefix_caching else 0))
         if not h:
             raise ValueError("CacheManager: bad sizes")

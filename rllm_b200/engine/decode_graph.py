@@ -168,7 +168,7 @@ class DecodeGraph:
             h[self.r_pos[0] + s] = e.start
             h[self.r_seqlens[0] + s] = e.start + 1
             h[self.r_slots[0] + s] = cache.slot(e.req)
-        windowed = any(cache.needs[g].window is not None for g in self.paged)
+        windowed = any(cache.needs[g].span is not None for g in self.paged)
         reqs = [e.req for e in entries]
         # a request is known by the number of its admission, not by its name: a name may come back (after
         # its request ended, or was preempted and admitted again) with other pages

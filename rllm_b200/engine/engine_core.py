@@ -89,7 +89,8 @@ def plan_cache_pages(model: DecoderModel, args: EngineArgs, max_model_len: int, 
     for g, need in enumerate(model.layout.groups):
         if not isinstance(need, KVPagesNeed):
             continue
-        per_request = full if need.window is None else min(full, -(-(need.window + portion) // bs) + 1)
+        per_request = full if need.span is None else \
+            min(full, -(-(need.span + portion) // bs) + 1 + -(-need.keep_first // bs))
         useful.append(args.max_num_seqs * per_request)
         nbytes.append(page_bytes(need, bs, elem) * len(model.layout.owners[g]))
     if not useful:
@@ -111,7 +112,7 @@ def plan_cache_pages(model: DecoderModel, args: EngineArgs, max_model_len: int, 
 
 
 def _windowed(model: DecoderModel) -> List[bool]:
-    return [need.window is not None for need in model.layout.groups if isinstance(need, KVPagesNeed)]
+    return [need.span is not None for need in model.layout.groups if isinstance(need, KVPagesNeed)]
 
 
 @dataclass(frozen=True)

@@ -146,7 +146,7 @@ class Scheduler:
         self.num_preemptions = 0
         self.prefix_hit_tokens = 0
         self.num_copied_tokens = 0          # tokens that requests took over from another by ``add_copy``
-        self._windowed = any(getattr(cache.needs[g], "window", None) is not None for g in cache.paged)
+        self._windowed = any(getattr(cache.needs[g], "span", None) is not None for g in cache.paged)
 
     # ------------------------------------------------------------------
     def add_request(self, req: Request) -> None:

@@ -12,6 +12,15 @@
 // scaled by `scale`; softmax is online in float32 (:159-169), P.V is
 // accumulated in float32 and divided by the sum once (:173-178).
 //
+// Options beyond that contract (each off at 0 / null):
+//   keep_first  with a window: keys 0 .. keep_first - 1 stay visible however far back they lie;
+//   chunk       the query sees only keys of its own chunk, floor(j / chunk) == floor(p / chunk);
+//   softcap     score <- softcap * tanh(score / softcap) after the scaling;
+//   sinks       float32 [nq]: exp(sinks[h]) joins the softmax's denominator (no key, no value, unscaled);
+//   gate        a row of gate pre-activations beside the token's queries: the result is multiplied by
+//               sigmoid(gate[h]) (gate_mode 1, one number a head) or sigmoid(gate[h * dv + i])
+//               (gate_mode 2, one a result element).
+//
 // Keys are walked in groups of 32 aligned to absolute positions, so the
 // arithmetic of a row does not depend on how the sequence was cut into steps,
 // on the batch around it, or on which pages hold it.
@@ -46,7 +55,8 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
                       const int* __restrict__ block_table, int max_blocks,
                       const int* __restrict__ positions, const int* __restrict__ token_seq, int T_tokens,
                       int nq, int nkv, int d, int dv, int page_size, int num_pages, int window, float scale,
-                      int* __restrict__ err) {
+                      int keep_first, int chunk, float softcap, const float* __restrict__ sinks,
+                      const T* __restrict__ gate, int gate_stride, int gate_mode, int* __restrict__ err) {
   extern __shared__ float qs[];  // [ATT_WARPS][d]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long gw = (long long)blockIdx.x * ATT_WARPS + warp;
@@ -56,7 +66,12 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
   const int s = token_seq[t];
   const int qpos = positions[t];
   const int kend = qpos + 1;
-  const int kstart = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
+  int kstart = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
+  if (chunk > 0) kstart = max(kstart, qpos / chunk * chunk);
+  // the kept first keys that lie ahead of the recent ones: a range of their own, walked first
+  const int kept_end = (window > 0 && keep_first > 0) ? min(min(keep_first, kstart), kend) : 0;
+  const int kept_start = (chunk > 0) ? min(qpos / chunk * chunk, kept_end) : 0;
+  const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
   float* myq = qs + warp * d;
   const T* qrow = q + (size_t)t * q_stride + (size_t)h * d;
   for (int i = lane; i < d; i += 32) myq[i] = to_f32(qrow[i]);
@@ -68,9 +83,11 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
   for (int r = 0; r < ATT_MAX_D / 32; ++r) acc[r] = 0.f;
   const int* bt = block_table + (size_t)s * max_blocks;
 
-  for (int j0 = (kstart / 32) * 32; j0 < kend; j0 += 32) {
+  for (int range = 0; range < 2; ++range) {
+  const int lo = range == 0 ? kept_start : kstart, hi = range == 0 ? kept_end : kend;
+  for (int j0 = (lo / 32) * 32; j0 < hi; j0 += 32) {
     const int j = j0 + lane;
-    const bool valid = (j >= kstart) && (j < kend);
+    const bool valid = (j >= lo) && (j < hi);
     float score = -INFINITY;
     int page = -1;
     if (valid) {
@@ -92,6 +109,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
           for (int i = 0; i < d; ++i) dot = fmaf(myq[i], to_f32(kp[i]), dot);
         }
         score = dot * scale;
+        if (softcap > 0.f) score = softcap * tanhf(score * inv_cap);
       }
     }
     const float cmax = warp_max(score);
@@ -103,8 +121,8 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
 #pragma unroll
     for (int r = 0; r < ATT_MAX_D / 32; ++r) acc[r] *= corr;
     m = m_new;
-    const int jn = min(32, kend - j0);
-    for (int jj = max(0, kstart - j0); jj < jn; ++jj) {
+    const int jn = min(32, hi - j0);
+    for (int jj = max(0, lo - j0); jj < jn; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const int pg = __shfl_sync(0xffffffffu, page, jj);
       if (pg < 0) continue;
@@ -116,12 +134,27 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
       }
     }
   }
+  }
+  if (sinks) {                                   // one more term of the denominator
+    const float sk = sinks[h];
+    const float m_new = fmaxf(m, sk);
+    const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
+    l = l * corr + expf(sk - m_new);
+#pragma unroll
+    for (int r = 0; r < ATT_MAX_D / 32; ++r) acc[r] *= corr;
+  }
   T* orow = out + ((size_t)t * nq + h) * dv;
-  const float inv = (l > 0.f) ? 1.0f / l : 0.f;
+  float inv = (l > 0.f) ? 1.0f / l : 0.f;
+  const T* grow = gate_mode ? gate + (size_t)t * gate_stride : nullptr;
+  if (gate_mode == 1) inv *= 1.0f / (1.0f + expf(-to_f32(grow[h])));
 #pragma unroll
   for (int r = 0; r < ATT_MAX_D / 32; ++r) {
     const int i = lane + 32 * r;
-    if (i < dv) orow[i] = from_f32<T>(acc[r] * inv);
+    if (i < dv) {
+      float v = acc[r] * inv;
+      if (gate_mode == 2) v *= 1.0f / (1.0f + expf(-to_f32(grow[(size_t)h * dv + i])));
+      orow[i] = from_f32<T>(v);
+    }
   }
 }
 
@@ -130,10 +163,13 @@ RLLM_EXPORT int rllm_attention_simt_kv(const void* q, int q_stride, void* out, c
                                        const void* vcache, int dtype, const int* block_table,
                                        int max_blocks, const int* positions, const int* token_seq, int T,
                                        int nq, int nkv, int d, int dv, int page_size, int num_pages, int window,
-                                       float scale, int* err, cudaStream_t stream) {
+                                       float scale, int keep_first, int chunk, float softcap, const float* sinks,
+                                       const void* gate, int gate_stride, int gate_mode, int* err,
+                                       cudaStream_t stream) {
   if (T <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || dv <= 0 || page_size <= 0 || num_pages <= 0 ||
-      max_blocks <= 0 || window < 0)
+      max_blocks <= 0 || window < 0 || keep_first < 0 || chunk < 0 || !(softcap >= 0.f) || gate_mode < 0 ||
+      gate_mode > 2 || (gate_mode && !gate))
     return RLLM_E_BADARG;
   if (dv > ATT_MAX_D || d > 1024) return RLLM_E_UNSUPPORTED;
   const bool vec = d % 8 == 0 && q_stride % 8 == 0 && (((uintptr_t)q | (uintptr_t)kcache) & 31) == 0;
@@ -144,7 +180,8 @@ RLLM_EXPORT int rllm_attention_simt_kv(const void* q, int q_stride, void* out, c
   RLLM_DISPATCH_DTYPE(dtype, T_,                                                                            \
     (attention_simt_kernel<T_, VEC_><<<blocks, 32 * ATT_WARPS, smem, stream>>>(                             \
         (const T_*)q, q_stride, (T_*)out, (const T_*)kcache, (const T_*)vcache, block_table,                \
-        max_blocks, positions, token_seq, T, nq, nkv, d, dv, page_size, num_pages, window, scale, err)))
+        max_blocks, positions, token_seq, T, nq, nkv, d, dv, page_size, num_pages, window, scale, keep_first,  \
+        chunk, softcap, sinks, (const T_*)gate, gate_stride, gate_mode, err)))
   if (vec) ATT_GO(true); else ATT_GO(false);
 #undef ATT_GO
   RLLM_LAUNCH_CHECK();
@@ -159,5 +196,6 @@ RLLM_EXPORT int rllm_attention_simt(const void* q, int q_stride, void* out, cons
   if (d % 16 != 0 || d > ATT_MAX_D) return d > 0 ? RLLM_E_UNSUPPORTED : RLLM_E_BADARG;  // head sizes in steps of 16, to 256
   if (q_stride % 8 != 0) return RLLM_E_BADARG;
   return rllm_attention_simt_kv(q, q_stride, out, kcache, vcache, dtype, block_table, max_blocks, positions,
-                                token_seq, T, nq, nkv, d, d, page_size, num_pages, window, scale, err, stream);
+                                token_seq, T, nq, nkv, d, d, page_size, num_pages, window, scale, 0, 0, 0.f, nullptr,
+                                nullptr, 0, 0, err, stream);
 }

@@ -7,7 +7,11 @@
 //                        rest of a row is written as zeros, and the queries then go, padded with
 //                        zeros to dkp a head, into a buffer of their own.  (Zeros change no score
 //                        and add columns of zeros to the result: keys and values of two sizes
-//                        can so be served by kernels that want one.)
+//                        can so be served by kernels that want one.)  Optional steps on the way, in this
+//                        order: a bias on every element of the row (float32 [nq dk + nkv dk + nkv dv]), the
+//                        norm, and a rotation of queries and keys by position over the first rd dims of a
+//                        head (dimension i with i + rd / 2, angle position * inv_freq[i], cosine and sine
+//                        times `mag`; float32 rows take them in float64).
 //   rms_mean             out = (1/n) sum_i rms(x_i) * w_i  over n = 2 inputs of one width
 //                        (branches of a mixer that run side by side)
 //   gated_rmsnorm        out = rms(x) * w * sigmoid(g)     (x float32, g in the activation dtype)
@@ -25,7 +29,8 @@ __global__ void __launch_bounds__(32 * HN_WARPS)
 head_norm_kv_write_kernel(T* qkv, int stride, const int* positions, const int* token_seq, const TW* wq, const TW* wk,
                           float eps, const int* block_table, int max_blocks, T* kcache, T* vcache, int T_tokens, int nq,
                           int nkv, int dk, int dv, int dkp, int dvp, T* q_out, int page_size, int num_pages,
-                          int write_kv, int* err) {
+                          int write_kv, const float* __restrict__ bias, const double* __restrict__ inv_freq, int rd,
+                          float mag, int* err) {
   pdl_wait();
   pdl_launch();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -35,9 +40,10 @@ head_norm_kv_write_kernel(T* qkv, int stride, const int* positions, const int* t
   const int t = (int)(gw / heads), h = (int)(gw - (long long)t * heads);
   T* row = qkv + (size_t)t * stride;
   T* dst = nullptr;
+  const int pos = positions[t];
   if (h >= nq) {
     if (!write_kv) return;
-    const int pos = positions[t], s = token_seq[t];
+    const int s = token_seq[t];
     const int blk = pos / page_size;
     const int page = (blk < max_blocks) ? block_table[(size_t)s * max_blocks + blk] : -1;
     if (page < 0 || page >= num_pages) {
@@ -50,33 +56,62 @@ head_norm_kv_write_kernel(T* qkv, int stride, const int* positions, const int* t
   } else if (q_out) {
     dst = q_out + ((size_t)t * nq + h) * dkp;
   }
-  if (h >= nq + nkv) {                                    // a value head: copied as it is
-    const T* src = row + (size_t)nq * dk + (size_t)nkv * dk + (size_t)(h - nq - nkv) * dv;
-    for (int i = lane; i < dvp; i += 32) dst[i] = (i < dv) ? src[i] : from_f32<T>(0.f);
+  if (h >= nq + nkv) {                                    // a value head: copied (with its bias)
+    const size_t at = (size_t)nq * dk + (size_t)nkv * dk + (size_t)(h - nq - nkv) * dv;
+    const T* src = row + at;
+    for (int i = lane; i < dvp; i += 32)
+      dst[i] = (i >= dv) ? from_f32<T>(0.f) : (bias ? from_f32<T>(to_f32(src[i]) + bias[at + i]) : src[i]);
     return;
   }
   T* src = row + (size_t)h * dk;                          // query heads, then key heads: both dk wide
+  const float* bs = bias ? bias + (size_t)h * dk : nullptr;
   const TW* w = (h < nq) ? wq : wk;
-  if (!w) {
+  if (!w && !bs && rd == 0) {
     if (dst) for (int i = lane; i < dkp; i += 32) dst[i] = (i < dk) ? src[i] : from_f32<T>(0.f);
     return;
   }
-  float ss = 0.f;
-  for (int i = lane; i < dk; i += 32) { const float v = to_f32(src[i]); ss = fmaf(v, v, ss); }
-  ss = warp_sum(ss);
-  const float r = 1.0f / sqrtf(ss / (float)dk + eps);
+  float r = 1.0f;
+  if (w) {
+    float ss = 0.f;
+    for (int i = lane; i < dk; i += 32) { const float v = to_f32(src[i]) + (bs ? bs[i] : 0.f); ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    r = 1.0f / sqrtf(ss / (float)dk + eps);
+  }
   T* o = dst ? dst : src;
-  for (int i = lane; i < (dst ? dkp : dk); i += 32)
-    o[i] = (i < dk) ? from_f32<T>(to_f32(src[i]) * r * to_f32(w[i])) : from_f32<T>(0.f);
+  const int half = rd >> 1;
+  // a lane reads both members of its pairs before it writes them, and no other lane touches them: in place is safe
+  for (int i = lane; i < half; i += 32) {
+    float a = to_f32(src[i]) + (bs ? bs[i] : 0.f), b = to_f32(src[i + half]) + (bs ? bs[i + half] : 0.f);
+    if (w) { a *= r * to_f32(w[i]); b *= r * to_f32(w[i + half]); }
+    float c, sn;
+    if (sizeof(T) == 4) {
+      double sd, cd;
+      sincos((double)pos * inv_freq[i], &sd, &cd);
+      c = (float)(cd * (double)mag); sn = (float)(sd * (double)mag);
+    } else {
+      rope_cos_sin(pos, inv_freq[i], &c, &sn);
+      c *= mag; sn *= mag;
+    }
+    o[i] = from_f32<T>(a * c - b * sn);
+    o[i + half] = from_f32<T>(b * c + a * sn);
+  }
+  for (int i = rd + lane; i < (dst ? dkp : dk); i += 32) {
+    if (i >= dk) { o[i] = from_f32<T>(0.f); continue; }
+    float a = to_f32(src[i]) + (bs ? bs[i] : 0.f);
+    if (w) a *= r * to_f32(w[i]);
+    o[i] = from_f32<T>(a);
+  }
 }
 
 RLLM_EXPORT int rllm_head_norm_kv_write(void* qkv, int dtype, int stride, const int* positions, const int* token_seq,
                                         const void* wq, const void* wk, int w_dtype, float eps, const int* block_table,
                                         int max_blocks, void* kcache, void* vcache, int T, int nq, int nkv, int dk,
                                         int dv, int dkp, int dvp, void* q_out, int page_size, int num_pages,
-                                        int write_kv, int* err, cudaStream_t stream) {
+                                        int write_kv, const float* bias, const double* inv_freq, int rd, float mag,
+                                        int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (nq <= 0 || nkv < 0 || dk <= 0 || dv <= 0 || dkp < dk || dvp < dv) return RLLM_E_BADARG;
+  if (rd < 0 || rd > dk || (rd & 1) || (rd > 0 && !inv_freq)) return RLLM_E_BADARG;
   if (dkp > dk && !q_out) return RLLM_E_BADARG;          // padded keys want padded queries
   if (write_kv && (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !kcache || !vcache)) return RLLM_E_BADARG;
   const long long warps = (long long)T * (nq + 2 * nkv);
@@ -85,7 +120,7 @@ RLLM_EXPORT int rllm_head_norm_kv_write(void* qkv, int dtype, int stride, const 
     (rllm_launch_pdl(head_norm_kv_write_kernel<TT, TW>, dim3(blocks), dim3(32 * HN_WARPS), (size_t)0, stream, (TT*)qkv,
                      stride, positions, token_seq, (const TW*)wq, (const TW*)wk, eps, block_table, max_blocks,
                      (TT*)kcache, (TT*)vcache, T, nq, nkv, dk, dv, dkp, dvp, (TT*)q_out, page_size, num_pages,
-                     write_kv, err))));
+                     write_kv, bias, inv_freq, rd, mag, err))));
   RLLM_LAUNCH_CHECK();
   return 0;
 }

@@ -1066,14 +1066,23 @@ def head_norm_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: to
                        q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                        block_table: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, nq: int, nkv: int,
                        dk: int, dv: int, err: torch.Tensor, write_kv: bool = True,
-                       q_out: Optional[torch.Tensor] = None) -> None:
+                       q_out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                       inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0, magnitude: float = 1.0) -> None:
     """qkv [T, nq dk + nkv dk + nkv dv]: every query head (in place) and key head is divided by its root mean
     square and multiplied by the weight [dk] (None: left as it is); keys and values go to the token's place in
     kcache [pages, nkv, page, dkp] and vcache [pages, nkv, page, dvp].  Cache rows wider than the heads (dkp > dk,
-    dvp > dv) are filled up with zeros; the queries then go to ``q_out`` [T, nq * dkp], filled up alike."""
+    dvp > dv) are filled up with zeros; the queries then go to ``q_out`` [T, nq * dkp], filled up alike.
+    ``bias`` float32 [nq dk + nkv dk + nkv dv] is added to every row first; ``inv_freq`` float64 [rotary_dim / 2]
+    with ``rotary_dim`` > 0 rotates the first rotary_dim dims of every query and key head by the token's position
+    (dimension i with i + rotary_dim / 2), cosine and sine times ``magnitude``.  Columns of qkv behind the
+    value heads are left alone."""
     lib = build.load_library("mixer_glue")
     T = qkv.shape[0]
-    assert qkv.shape[1] == nq * dk + nkv * (dk + dv) and qkv.stride(1) == 1
+    assert qkv.shape[1] >= nq * dk + nkv * (dk + dv) and qkv.stride(1) == 1
+    if bias is not None:
+        assert bias.dtype is torch.float32 and bias.is_contiguous() and bias.numel() == nq * dk + nkv * (dk + dv)
+    if rotary_dim:
+        assert inv_freq is not None and inv_freq.dtype is torch.float64 and inv_freq.numel() == rotary_dim // 2
     dkp = q_out.shape[1] // nq if q_out is not None else dk
     dvp = dv
     if q_out is not None:
@@ -1094,24 +1103,38 @@ def head_norm_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: to
                                        _ptr(kcache if write_kv else None), _ptr(vcache if write_kv else None),
                                        c_int(T), c_int(nq), c_int(nkv if write_kv else 0), c_int(dk), c_int(dv),
                                        c_int(dkp), c_int(dvp), _ptr(q_out),
-                                       c_int(page_size), c_int(pages), c_int(1 if write_kv else 0), _ptr(err),
-                                       _stream()), "head_norm_kv_write")
+                                       c_int(page_size), c_int(pages), c_int(1 if write_kv else 0), _ptr(bias),
+                                       _ptr(inv_freq if rotary_dim else None), c_int(rotary_dim), c_float(magnitude),
+                                       _ptr(err), _stream()), "head_norm_kv_write")
 
 
 def attention_simt_kv(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor,
                       block_table: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor, nq: int, nkv: int,
-                      window: int, scale: float, err: torch.Tensor) -> None:
+                      window: int, scale: float, err: torch.Tensor, keep_first: int = 0, chunk: int = 0,
+                      softcap: float = 0.0, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                      gate_per_head: bool = False) -> None:
     """``attention_simt`` where keys [pages, nkv, page, dk] and values [pages, nkv, page, dv] have sizes of their
-    own: q rows of nq * dk, out [T, nq * dv]; any dk, dv up to 256."""
+    own: q rows of nq * dk, out [T, nq * dv]; any dk, dv up to 256.  ``keep_first``: with a window, the first
+    that many keys of a sequence stay visible; ``chunk``: only keys of the query's own chunk of positions are;
+    ``softcap``: scores become softcap * tanh(score / softcap); ``sinks`` float32 [nq]: exp(sink) joins each
+    head's softmax denominator; ``gate`` [T, nq] (``gate_per_head``) or [T, nq * dv], a view with the rows'
+    stride: the result is multiplied by its sigmoid."""
     lib = build.load_library("attention_simt")
     T, dk, dv = out.shape[0], kcache.shape[3], vcache.shape[3]
     _contig(out, "out"); _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
     assert kcache.dtype is q.dtype and vcache.dtype is q.dtype and out.dtype is q.dtype and out.shape[1] == nq * dv
+    if sinks is not None:
+        assert sinks.dtype is torch.float32 and sinks.numel() == nq and sinks.is_contiguous()
+    if gate is not None:
+        assert gate.dtype is q.dtype and gate.stride(1) == 1 and gate.shape == (T, nq if gate_per_head else nq * dv)
     _check(lib.rllm_attention_simt_kv(_ptr(q), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache),
                                       c_int(dtype_code(q.dtype)), _ptr(block_table), c_int(block_table.shape[1]),
                                       _ptr(positions), _ptr(token_seq), c_int(T), c_int(nq), c_int(nkv), c_int(dk),
                                       c_int(dv), c_int(kcache.shape[2]), c_int(kcache.shape[0]), c_int(window),
-                                      c_float(scale), _ptr(err), _stream()), "attention_simt_kv")
+                                      c_float(scale), c_int(keep_first), c_int(chunk), c_float(softcap), _ptr(sinks),
+                                      _ptr(gate), c_int(gate.stride(0) if gate is not None else 0),
+                                      c_int(0 if gate is None else (1 if gate_per_head else 2)),
+                                      _ptr(err), _stream()), "attention_simt_kv")
 
 
 def rms_mean2(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float) -> torch.Tensor:
@@ -1225,3 +1248,52 @@ def selective_scan(xc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor
                                    c_int(num_seqs), c_int(chunks), _ptr(out), c_int(E), c_int(N), _ptr(err),
                                    _stream()), "selective_scan")
     return out
+
+
+# ---------------------------------------------------------------------------
+# layer norm over the float32 stream (layernorm.cu)
+# ---------------------------------------------------------------------------
+def layernorm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float, out: torch.Tensor,
+              deltas=(), row_bias: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+              writeback: bool = False) -> None:
+    """out = (v - mean) / sqrt(mean of squared deviations + eps) * weight + bias, row by row in float32, with
+    v = x + the sum of ``deltas`` (up to two [T, H] in out's dtype) + ``row_bias`` (float32 [H], every row).
+    ``writeback``: x becomes v.  ``rows`` int32 [R]: out[r] is made from row rows[r]."""
+    lib = build.load_library("layernorm")
+    H = x.shape[-1]
+    R = rows.numel() if rows is not None else x.shape[0]
+    assert x.dtype is torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape == (R, H)
+    assert weight.dtype is torch.float32 and bias.dtype is torch.float32 and weight.numel() == H and bias.numel() == H
+    deltas = tuple(deltas)
+    assert len(deltas) <= 2
+    for d in deltas:
+        assert d.dtype is out.dtype and d.shape == x.shape and d.is_contiguous()
+    if row_bias is not None:
+        assert row_bias.dtype is torch.float32 and row_bias.numel() == H and row_bias.is_contiguous()
+    d0 = deltas[0] if deltas else None
+    d1 = deltas[1] if len(deltas) > 1 else None
+    _check(lib.rllm_layernorm(_ptr(x), _ptr(d0), _ptr(d1), _ptr(row_bias), _ptr(rows), _ptr(weight), _ptr(bias),
+                              _ptr(out), c_int(dtype_code(out.dtype)), c_int(R), c_int(H), c_float(eps),
+                              c_int(1 if writeback else 0), _stream()), "layernorm")
+
+
+def add_rows(x: torch.Tensor, deltas, row_bias: Optional[torch.Tensor] = None) -> None:
+    """x (float32 [T, H]) += the sum of ``deltas`` (one or two [T, H]) + ``row_bias`` (float32 [H])."""
+    lib = build.load_library("layernorm")
+    deltas = tuple(deltas)
+    assert 1 <= len(deltas) <= 2 and x.dtype is torch.float32 and x.is_contiguous()
+    for d in deltas:
+        assert d.shape == x.shape and d.is_contiguous() and d.dtype is deltas[0].dtype
+    if row_bias is not None:
+        assert row_bias.dtype is torch.float32 and row_bias.numel() == x.shape[1] and row_bias.is_contiguous()
+    _check(lib.rllm_add_rows(_ptr(x), _ptr(deltas[0]), _ptr(deltas[1] if len(deltas) > 1 else None), _ptr(row_bias),
+                             c_int(dtype_code(deltas[0].dtype)), c_int(x.shape[0]), c_int(x.shape[1]), _stream()),
+           "add_rows")
+
+
+def add_row_bias(y: torch.Tensor, bias: torch.Tensor) -> None:
+    """y [T, N] (bfloat16 or float32) += ``bias`` (float32 [N]) on every row, in place."""
+    lib = build.load_library("layernorm")
+    assert y.dim() == 2 and y.is_contiguous() and bias.dtype is torch.float32 and bias.numel() == y.shape[1]
+    _check(lib.rllm_add_row_bias(_ptr(y), _ptr(bias), c_int(dtype_code(y.dtype)), c_int(y.shape[0]),
+                                 c_int(y.shape[1]), _stream()), "add_row_bias")

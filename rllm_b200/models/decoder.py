@@ -19,7 +19,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from ..parts import registry as part_registry
-from ..parts.base import KVCacheView, StateCacheView, StepContext
+from ..parts.base import KVCacheView, PendingSum, StateCacheView, StepContext
 from ..parts.embedding import OutputHead, TokenEmbedding
 from ..parts.spec import KVPagesNeed, ModelSpec, StateNeed, TensorSpec
 from ..weights.loader import WeightSource, load_tensors
@@ -177,11 +177,15 @@ class DecoderModel:
                 # the norm that reads the stream after this block: the block may prepare its input
                 nxt = getattr(self.blocks[order[i + 1].layer], "norms", None)
                 h, pending = block.forward(h, pending, ctx, storage.view(i), next_norm=nxt[0] if nxt else None)
+            elif getattr(block, "takes_final_norm", False) and self.spec.streams == 0:
+                # the last block, and one that wants to know: the model's own norm reads the stream next
+                h, pending = block.forward(h, pending, ctx, storage.view(i), next_norm=self.final_norm)
             else:
                 h, pending = block.forward(h, pending, ctx, storage.view(i))
         if logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=h.device)
-        if not isinstance(pending, torch.Tensor):
+        if not isinstance(pending, torch.Tensor) and not (
+                isinstance(pending, PendingSum) and getattr(self.final_norm, "takes_pending_sum", False)):
             pending = None                      # a block that adds into the stream itself left it complete
         if h.dim() == 3:
             # the output reads the sum of the streams; a norm without statistics joins that kernel

@@ -244,6 +244,8 @@ struct Manager {
   int num_groups, page_size, max_seqs;
   std::vector<int> kind;                    // 0: pages of keys and values, 1: state of fixed size
   std::vector<int> window;                  // per group; -1: all keys
+  std::vector<int> keep_first;              // per group: the first tokens of a sequence whose pages always stay
+  std::vector<int> chunk;                   // per group; > 0: a query needs only the keys of its own chunk
   std::vector<int> paged;                   // group indices with pages
   std::vector<Pool*> pools;                 // per group (null for state groups)
   std::unordered_map<int64_t, Req> reqs;
@@ -252,17 +254,27 @@ struct Manager {
 
   ~Manager() { for (Pool* p : pools) delete p; }
   Req* find(int64_t id) { auto it = reqs.find(id); return it == reqs.end() ? nullptr : &it->second; }
+  // The first page of the recent keys that queries from first_query_pos on can still see: the window's
+  // start, or the start of the query's chunk, whichever is later.
   int first_needed_page(int g, long long first_query_pos) const {
-    if (window[g] < 0) return 0;
-    const long long lo = first_query_pos - window[g] + 1;
-    return (int)((lo > 0 ? lo : 0) / page_size);
+    long long lo = 0;
+    if (window[g] >= 0 && first_query_pos - window[g] + 1 > lo) lo = first_query_pos - window[g] + 1;
+    if (chunk[g] > 0 && first_query_pos / chunk[g] * chunk[g] > lo) lo = first_query_pos / chunk[g] * chunk[g];
+    return (int)(lo / page_size);
+  }
+  // Pages 0 .. kept_pages - 1 hold the sequence's kept first tokens and are never given back.
+  int kept_pages(int g) const { return keep_first[g] > 0 ? (keep_first[g] + page_size - 1) / page_size : 0; }
+  // whether page k holds keys that queries from first_query_pos on can see
+  bool page_needed(int g, long long k, long long first_query_pos) const {
+    return k < kept_pages(g) || k >= first_needed_page(g, first_query_pos);
   }
   int release_behind_window(Req* r, long long first_query_pos) {
     int n = 0;
     for (int g : paged) {
       int upto = first_needed_page(g, first_query_pos);
       if (upto > (int)r->tables[g].size()) upto = (int)r->tables[g].size();
-      for (int k = r->released[g]; k < upto; ++k)
+      const int from = r->released[g] > kept_pages(g) ? r->released[g] : kept_pages(g);
+      for (int k = from; k < upto; ++k)
         if (r->tables[g][k] >= 0) { pools[g]->release(r->tables[g][k]); r->tables[g][k] = -1; ++n; }
       if (upto > r->released[g]) r->released[g] = upto;
     }
@@ -274,7 +286,7 @@ struct Manager {
   long long shareable_pages(const std::vector<Hash16>& hs) const {
     long long k = (long long)hs.size();
     for (int g : paged) {
-      if (window[g] >= 0) continue;
+      if (gives_back(g)) continue;
       long long have = 0;
       while (have < k && pools[g]->peek(hs[have]) >= 0) ++have;
       k = have;
@@ -282,7 +294,8 @@ struct Manager {
     for (; k > 0; --k) {
       bool ok = true;
       for (int g : paged) {
-        if (window[g] < 0) continue;
+        if (!gives_back(g)) continue;
+        for (long long j = 0; j < k && j < kept_pages(g) && ok; ++j) ok = pools[g]->peek(hs[j]) >= 0;
         for (long long j = first_needed_page(g, k * page_size); j < k && ok; ++j) ok = pools[g]->peek(hs[j]) >= 0;
         if (!ok) break;
       }
@@ -290,11 +303,19 @@ struct Manager {
     }
     return k;
   }
+  bool gives_back(int g) const { return window[g] >= 0 || chunk[g] > 0; }
+  // pages that ensure(first_query_pos, num_tokens) would take: those of the table's new entries that are needed
   int pages_needed(const Req* r, int g, long long first_query_pos, long long num_tokens) const {
     const long long want = (num_tokens + page_size - 1) / page_size;
+    const long long have = (long long)r->tables[g].size();
     long long first = first_needed_page(g, first_query_pos);
-    if ((long long)r->tables[g].size() > first) first = (long long)r->tables[g].size();
-    return (int)(want > first ? want - first : 0);
+    if (have > first) first = have;
+    long long n = want > first ? want - first : 0;
+    // kept first pages that lie ahead of the recent ones and are not in the table yet
+    long long kept = kept_pages(g) < first ? kept_pages(g) : first;
+    if (kept > want) kept = want;
+    if (kept > have) n += kept - have;
+    return (int)n;
   }
 };
 
@@ -343,8 +364,9 @@ API int rllm_pool_check(void* h, char* why, int cap) {
 
 // ---- manager ----
 // kinds[g]: 0 pages, 1 state; windows[g]: keys a query sees, or -1 for all; num_pages[g]: pages of a paged group
-API void* rllm_cache_new(int num_groups, const int* kinds, const int* windows, const int* num_pages, int page_size,
-                         int max_seqs, int enable_prefix_caching) {
+// keep_first[g], chunks[g] (either array may be null: none): see Manager
+API void* rllm_cache_new(int num_groups, const int* kinds, const int* windows, const int* keep_first, const int* chunks,
+                         const int* num_pages, int page_size, int max_seqs, int enable_prefix_caching) {
   if (num_groups < 0 || page_size < 1 || max_seqs < 1) return nullptr;
   Manager* m = new Manager();
   m->num_groups = num_groups; m->page_size = page_size; m->max_seqs = max_seqs;
@@ -352,6 +374,8 @@ API void* rllm_cache_new(int num_groups, const int* kinds, const int* windows, c
   for (int g = 0; g < num_groups; ++g) {
     m->kind.push_back(kinds[g]);
     m->window.push_back(windows[g]);
+    m->keep_first.push_back(keep_first && windows[g] >= 0 && keep_first[g] > 0 ? keep_first[g] : 0);
+    m->chunk.push_back(chunks && chunks[g] > 0 ? chunks[g] : 0);
     if (kinds[g] == 0) {
       if (num_pages[g] < 1) { delete m; return nullptr; }
       m->paged.push_back(g);
@@ -435,8 +459,8 @@ API int rllm_cache_fork(void* h, int64_t parent_id, int64_t child_id, long long 
   for (int g : m->paged) {
     if ((long long)p->tables[g].size() < want) return RC_NOT_HELD;       // the parent does not hold that much
     // a window may have passed pages that the child's next query (at position num_tokens) would still see
-    for (long long k = m->first_needed_page(g, num_tokens); k < want; ++k)
-      if (p->tables[g][k] < 0) return RC_NOT_HELD;
+    for (long long k = 0; k < want; ++k)
+      if (m->page_needed(g, k, num_tokens) && p->tables[g][k] < 0) return RC_NOT_HELD;
     if (partial && p->tables[g][want - 1] >= 0) {
       if (m->pools[g]->num_free() < 1) return -1;
       ++n_copy;
@@ -516,7 +540,7 @@ API int rllm_cache_ensure(void* h, int64_t id, long long first_query_pos, long l
     const int first = m->first_needed_page(g, first_query_pos);
     while ((long long)r->tables[g].size() < want) {
       const int k = (int)r->tables[g].size();
-      if (k < first) {            // behind the window from the start: never held
+      if (k < first && k >= m->kept_pages(g)) {   // behind the window from the start: never held
         r->tables[g].push_back(-1);
         r->released[g] = k + 1;
       } else {
@@ -535,9 +559,13 @@ API long long rllm_cache_max_tokens(void* h, int64_t id, long long first_query_p
   m->release_behind_window(r, first_query_pos);
   long long best = -1;
   for (int g : m->paged) {
+    const long long have = (long long)r->tables[g].size();
     long long first = m->first_needed_page(g, first_query_pos);
-    if ((long long)r->tables[g].size() > first) first = (long long)r->tables[g].size();
-    const long long upto = (first + m->pools[g]->num_free()) * m->page_size;
+    if (have > first) first = have;
+    long long kept = m->kept_pages(g) < first ? m->kept_pages(g) : first;     // kept first pages still to take
+    kept = kept > have ? kept - have : 0;
+    const long long room = m->pools[g]->num_free() - kept;
+    const long long upto = room < 0 ? have * m->page_size : (first + room) * m->page_size;
     if (best < 0 || upto < best) best = upto;
   }
   return best < 0 ? (1LL << 62) : best;
@@ -547,8 +575,10 @@ API int rllm_cache_fits_at_all(void* h, long long num_tokens) {
   const long long want = (num_tokens + m->page_size - 1) / m->page_size;
   for (int g : m->paged) {
     long long want_g = want;
-    if (m->window[g] >= 0) {
-      const long long w = (m->window[g] + m->page_size + m->page_size - 1) / m->page_size + 1;
+    if (m->gives_back(g)) {
+      long long span = m->window[g] >= 0 ? m->window[g] : m->chunk[g];
+      if (m->chunk[g] > 0 && m->chunk[g] < span) span = m->chunk[g];
+      const long long w = (span + m->page_size + m->page_size - 1) / m->page_size + 1 + m->kept_pages(g);
       if (w < want_g) want_g = w;
     }
     if (want_g > m->pools[g]->n) return 0;
@@ -581,7 +611,7 @@ API long long rllm_cache_adopt_prefix(void* h, int64_t id, const int64_t* tokens
   for (int g : m->paged) {
     const long long first = m->first_needed_page(g, got * m->page_size);
     for (long long k = 0; k < got; ++k)
-      r->tables[g].push_back(k < first ? -1 : m->pools[g]->acquire_cached(hs[k]));
+      r->tables[g].push_back(k < first && k >= m->kept_pages(g) ? -1 : m->pools[g]->acquire_cached(hs[k]));
     r->released[g] = (int)(first < got ? first : got);
   }
   hs.resize((size_t)got);

@@ -19,12 +19,23 @@ a query and key head (the output projection then reads num_heads * v_dim), and
 mean square (eps inside the root) and multiplied by a weight [head_dim] that
 all heads share (tensor names "q_norm", "k_norm").  With either, the tokens'
 keys (normalised) and values are written to the pages by one kernel and the
-attention reads everything from there; these two take no rotation.
+attention reads everything from there.
+
+More options, each with its constants as parameters; a mixer with any of them goes the same way (one
+kernel adds the biases, normalises, rotates and writes the pages; the attention reads from the pages):
+``bias`` True: q, k, v and the output projection have biases ("q_bias", "k_bias", "v_bias", "o_bias"),
+added in float32; ``softcap`` = c: a scaled score s becomes c tanh(s / c); ``chunk`` = n: a query at
+position p sees only keys j with floor(j / n) = floor(p / n), counted from the sequence's position 0;
+``keep_first`` = n (with ``window``): keys 0 .. n-1 stay visible behind the window, at their true
+positions; ``sinks`` True: exp(sink[h]) ("sink", one number a head) joins the softmax's denominator, with
+no key and no value; ``gate`` "head" or "element": the heads' outputs are multiplied by sigmoid(W_g x)
+("g": [num_heads, hidden] or [num_heads * v_dim, hidden]) before the output projection; W_g is stacked
+under [Wq; Wk; Wv], so the gate comes out of the same product.
 
 params: hidden_size, num_heads, num_kv_heads, head_dim, window (None: all
 keys), scale (None: 1/sqrt(head_dim)), position (PartSpec), shares_kv (True:
 the run reads another run's cache, has no k/v projections and writes nothing),
-v_dim (None: head_dim), qk_norm (None, or eps),
+v_dim (None: head_dim), qk_norm (None, or eps), bias, softcap, chunk, keep_first, sinks, gate,
 tensor_names (the names of the four projection weights below the part's prefix,
 keys "q", "k", "v", "o", with qk_norm also "q_norm", "k_norm": the architecture
 gives them, the part knows none).
@@ -62,14 +73,29 @@ class PagedAttention(Mixer):
         self.shares_kv = bool(p.get("shares_kv", False))
         self.dv = int(p.get("v_dim") or self.d)
         self.qk_eps = float(p["qk_norm"]) if p.get("qk_norm") is not None else None
-        self.plain = self.dv == self.d and self.qk_eps is None      # the Llama's form: rotation fused with the write
+        self.bias = bool(p.get("bias", False))
+        self.softcap = float(p["softcap"]) if p.get("softcap") else 0.0
+        self.chunk = int(p["chunk"]) if p.get("chunk") else 0
+        self.keep_first = int(p.get("keep_first") or 0)
+        self.sinks = bool(p.get("sinks", False))
+        self.gate = p.get("gate")
+        if self.gate not in (None, "head", "element"):
+            raise ValueError(f"gate {self.gate!r}; known: None, 'head', 'element'")
+        if self.keep_first and self.window is None:
+            raise ValueError("keep_first goes with a window")
+        if self.softcap < 0 or self.chunk < 0 or self.keep_first < 0:
+            raise ValueError("softcap, chunk and keep_first must not be negative")
+        # what the kernels of the Llama's form do not have: these go through the pages
+        self.masked = bool(self.softcap or self.chunk or self.keep_first or self.sinks or self.gate)
+        # the Llama's form: rotation fused with the write
+        self.plain = self.dv == self.d and self.qk_eps is None and not self.bias and not self.masked
         # keys and values of two sizes: where the larger one is a size of the tensor-core kernels, the pages keep
         # rows of that size for both (the rest zeros: no score changes, the result gains columns of zeros), and
         # those kernels serve; twice the pages' bytes for the smaller of the two against CUDA-core attention
         import os
         self.dp = max(self.d, self.dv)
         if self.d == self.dv or self.dp not in (16, 32, 64, 128) or self.nq // max(1, self.nkv) > 16 or \
-                os.environ.get("RLLM_ATTENTION_PAD") == "0":
+                self.masked or os.environ.get("RLLM_ATTENTION_PAD") == "0":
             self.dp = 0
         if self.nq % self.nkv:
             raise ValueError(f"num_heads {self.nq} must be a multiple of num_kv_heads {self.nkv}")
@@ -78,7 +104,9 @@ class PagedAttention(Mixer):
         if self.dv > 256:
             raise ValueError(f"v_dim {self.dv}: the attention kernels take value heads up to 256")
         names = dict(p.get("tensor_names") or ())
-        want = ["k", "o", "q", "v"] + (["k_norm", "q_norm"] if self.qk_eps is not None else [])
+        want = ["k", "o", "q", "v"] + (["k_norm", "q_norm"] if self.qk_eps is not None else []) + \
+            (["q_bias", "k_bias", "v_bias", "o_bias"] if self.bias else []) + (["sink"] if self.sinks else []) + \
+            (["g"] if self.gate else [])
         if sorted(names) != sorted(want):
             raise ValueError(f"an attention spec names its weights: tensor_names with the keys {sorted(want)}")
         self.names = {k: str(v) for k, v in names.items()}
@@ -87,9 +115,13 @@ class PagedAttention(Mixer):
                                    prefix=prefix)
         if getattr(self.position, "interleaved", False):
             raise ValueError("this mixer's kernels rotate halves; an interleaved rotation is not among them")
-        if not self.plain and pos is not None and pos.kind != "none":
-            raise ValueError("attention with v_dim or qk_norm takes no position encoding")
+        if not self.plain and self.position.fused_rotary() is None:
+            raise ValueError("attention through the pages takes a rotation that its kernel can apply, or none")
+        if self.shares_kv and (self.bias or self.gate):
+            raise ValueError("a run that reads another's keys and values takes no biases and no gate")
+        self.gate_width = 0 if not self.gate else (self.nq if self.gate == "head" else self.nq * self.dv)
         self.w_qn = self.w_kn = None
+        self.b_qkv = self.b_o = self.sink = None
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
 
@@ -114,6 +146,14 @@ class PagedAttention(Mixer):
             if not self.shares_kv:
                 specs.append(TensorSpec(self.prefix + self.names["k_norm"], (self.d,), role="vector",
                                         init=("one_plus_normal", 0.1)))
+        if self.bias:
+            for key, n in (("q_bias", self.nq * self.d), ("k_bias", self.nkv * self.d), ("v_bias", self.nkv * self.dv),
+                           ("o_bias", self.hidden)):
+                specs.append(TensorSpec(self.prefix + self.names[key], (n,), role="vector", init=("normal", 0.1)))
+        if self.sinks:
+            specs.append(TensorSpec(self.prefix + self.names["sink"], (self.nq,), role="vector", init=("normal", 1.0)))
+        if self.gate:
+            specs.append(TensorSpec(self.prefix + self.names["g"], (self.gate_width, self.hidden)))
         return specs
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -122,8 +162,17 @@ class PagedAttention(Mixer):
             self.w_qkv = tensors[q]
         else:
             # stacked [Wq; Wk; Wv]: one matrix product gives a token's q, k and v side by side
-            self.w_qkv = torch.cat([tensors[q], tensors[k], tensors[v]], dim=0).contiguous()
+            # (with a gate: [Wq; Wk; Wv; Wg], and the gate's pre-activations lie behind the value heads)
+            stack = [tensors[q], tensors[k], tensors[v]] + ([tensors[self.prefix + self.names["g"]]] if self.gate else [])
+            self.w_qkv = torch.cat(stack, dim=0).contiguous()
         self.w_o = tensors[o]
+        if self.bias:
+            # biases and sinks enter float32 arithmetic: kept so, whatever the run's dtype
+            self.b_qkv = torch.cat([tensors[self.prefix + self.names[key]].float()
+                                    for key in ("q_bias", "k_bias", "v_bias")]).contiguous()
+            self.b_o = tensors[self.prefix + self.names["o_bias"]].float().contiguous()
+        if self.sinks:
+            self.sink = tensors[self.prefix + self.names["sink"]].float().contiguous()
         if self.dp and self.dv < self.dp:
             # the attention's result has dp columns a head, the last ones zeros: the projection skips them
             w = self.w_o.new_zeros((self.hidden, self.nq, self.dp))
@@ -137,7 +186,8 @@ class PagedAttention(Mixer):
     def cache_need(self):
         if self.dp:
             return KVPagesNeed(self.nkv, self.dp, self.window)
-        return KVPagesNeed(self.nkv, self.d, self.window, v_dim=None if self.dv == self.d else self.dv)
+        return KVPagesNeed(self.nkv, self.d, self.window, v_dim=None if self.dv == self.d else self.dv,
+                           keep_first=self.keep_first, chunk=self.chunk or None)
 
     # -- compute ----------------------------------------------------------
     def fused_residual(self, num_rows: int, dtype: torch.dtype) -> bool:
@@ -152,15 +202,17 @@ class PagedAttention(Mixer):
         table = ctx.block_tables[cache.group]
         writes = cache.writes and not self.shares_kv
         q_pad = torch.empty((T, self.nq * self.dp), dtype=qkv.dtype, device=qkv.device) if self.dp else None
+        inv_freq, rd = self.position.fused_rotary(qkv.device)
         ops.head_norm_kv_write(qkv, ctx.positions, ctx.token_seq, self.w_qn, self.w_kn, self.qk_eps or 0.0, table,
                                cache.k, cache.v, self.nq, 0 if self.shares_kv else self.nkv, self.d, self.dv,
-                               ctx.err, write_kv=writes, q_out=q_pad)
+                               ctx.err, write_kv=writes, q_out=q_pad, bias=self.b_qkv, inv_freq=inv_freq,
+                               rotary_dim=rd, magnitude=float(getattr(self.position, "magnitude", 1.0)))
         d, dv = (self.dp, self.dp) if self.dp else (self.d, self.dv)
         if q_pad is not None:
             qkv = q_pad
         out = torch.empty((T, self.nq * dv), dtype=qkv.dtype, device=qkv.device)
         window, stride = int(self.window or 0), qkv.shape[1]
-        if dv == d and d % 16 == 0 and ops.use_mma_attention(qkv.dtype, self.nq, self.nkv, d):
+        if not self.masked and dv == d and d % 16 == 0 and ops.use_mma_attention(qkv.dtype, self.nq, self.nkv, d):
             nd = ctx.num_decode
             if nd:
                 ops.attention_decode_bf16(qkv, stride, out, cache.k, cache.v, table, ctx.seq_lens, nd,
@@ -176,13 +228,26 @@ class PagedAttention(Mixer):
                                                nd, ctx.num_seqs, T - nd, self.nq, self.nkv, d, window,
                                                self.scale, ctx.err)
             return out
+        gate = None
+        if self.gate:
+            at = self.nq * self.d + self.nkv * (self.d + self.dv)
+            gate = qkv[:, at: at + self.gate_width]
         ops.attention_simt_kv(qkv, stride, out, cache.k, cache.v, table, ctx.positions, ctx.token_seq, self.nq,
-                              self.nkv, window, self.scale, ctx.err)
+                              self.nkv, window, self.scale, ctx.err, keep_first=self.keep_first, chunk=self.chunk,
+                              softcap=self.softcap, sinks=self.sink, gate=gate, gate_per_head=self.gate == "head")
         return out
 
-    def forward(self, x, ctx: StepContext, cache: KVCacheView, residual=None):
-        out = self.attend(linear(x, self.w_qkv), ctx, cache)          # qkv [T, (nq + 2 nkv) d]
-        return linear(out, self.w_o, residual=residual)
+    def deferred_output_bias(self) -> Optional[torch.Tensor]:
+        """The output projection's bias (float32 [hidden]) for a block that adds it where it completes the
+        stream (it then calls ``forward`` with ``add_output_bias=False``); None: there is none."""
+        return self.b_o
+
+    def forward(self, x, ctx: StepContext, cache: KVCacheView, residual=None, add_output_bias: bool = True):
+        out = self.attend(linear(x, self.w_qkv), ctx, cache)          # qkv [T, (nq + 2 nkv) d (+ the gate's)]
+        y = linear(out, self.w_o, residual=residual)
+        if self.b_o is not None and add_output_bias:
+            ops.add_row_bias(y, self.b_o)
+        return y
 
     def attend(self, qkv: torch.Tensor, ctx: StepContext, cache: KVCacheView) -> torch.Tensor:
         """From the tokens' projections (q, k and v heads side by side) to the attention's output

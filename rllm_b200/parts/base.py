@@ -20,7 +20,9 @@ Mixer           cache_need() -> KVPagesNeed | StateNeed | None, or a tuple of ne
 FeedForward     forward(x act[T,H]) -> act[T,H]
 Block           forward(h_f32[T,H], pending act[T,H]|None, ctx, cache) -> (h_f32, pending)
                 where the true hidden state is h + pending (the last add is
-                left to the next norm, which fuses it)
+                left to the next norm, which fuses it); ``pending`` may be a
+                ``PendingSum`` (several terms) where the norm that reads the
+                stream next says it takes one
 
 Few rows (decoding): the residual stream without norm kernels
 -------------------------------------------------------------
@@ -113,6 +115,16 @@ class PreparedInput:
 
     x: torch.Tensor
     key: object
+
+
+@dataclass
+class PendingSum:
+    """The stream is h + the sum of ``terms`` (sublayer results [T, H] in the activation dtype, at most two)
+    + ``bias`` on every row (float32 [H], or None).  Only a norm that sets ``takes_pending_sum`` is handed
+    one (it completes the stream in the kernel that normalises); a block checks that before it leaves one."""
+
+    terms: Tuple[torch.Tensor, ...]
+    bias: Optional[torch.Tensor] = None
 
 
 @dataclass

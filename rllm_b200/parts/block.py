@@ -13,6 +13,13 @@ With few rows (decoding) and parts that can do it, no norm kernel runs at all:
 the product that ends the mixer (and the feed-forward) adds into h itself and
 leaves what the next norm needs, and the product that follows the norm applies
 it (see ``RowSumsq`` and ``ScaledRows`` in ``parts/base.py``).
+
+``parallel_residual`` has one norm that both sublayers read:
+    u   = norm_0(x)
+    out = x + (mixer(u) + ffn(u))
+(the feed-forward may be absent).  Neither add is done here where the norm that
+reads the stream next can take both results at once (``PendingSum``): that
+norm's kernel completes the stream, in float32, and normalises it.
 """
 from __future__ import annotations
 
@@ -20,7 +27,7 @@ from typing import List, Optional, Tuple
 
 import torch
 
-from .base import FeedForward, Mixer, Norm, RowSumsq, StepContext
+from .base import FeedForward, Mixer, Norm, PendingSum, RowSumsq, StepContext
 from .registry import register_part
 
 
@@ -64,3 +71,42 @@ class PreNormBlock:
         a = self.mixer.forward(xn, ctx, cache)
         xn = self.norms[1].add_forward(h, a)
         return h, self.ffn.forward(xn)
+
+
+@register_part("block", "parallel_residual")
+class ParallelResidualBlock:
+    def __init__(self, mixer: Mixer, ffn: Optional[FeedForward], norms: List[Norm]):
+        if len(norms) != 1:
+            raise ValueError("a parallel_residual block has one norm, read by the mixer and the feed-forward")
+        self.mixer, self.ffn, self.norms = mixer, ffn, norms
+
+    def parts(self):
+        return [self.norms[0], self.mixer] + ([self.ffn] if self.ffn is not None else [])
+
+    takes_next_norm = True
+    takes_final_norm = True      # the last block of a model is handed the model's own norm as the next one
+
+    def forward(self, h: torch.Tensor, pending, ctx: StepContext, cache, next_norm=None):
+        norm = self.norms[0]
+        if isinstance(pending, PendingSum) and not getattr(norm, "takes_pending_sum", False):
+            from ..kernels import ops
+            ops.add_rows(h, pending.terms, pending.bias)
+            pending = None
+        if isinstance(pending, (torch.Tensor, PendingSum)):
+            u = norm.add_forward(h, pending)
+        else:
+            u = norm.forward(h, ctx.act_dtype)           # h is complete
+        # a mixer that ends in a bias on every row may leave it to whoever completes the stream
+        defer = getattr(self.mixer, "deferred_output_bias", None)
+        bias = defer() if defer is not None else None
+        a = self.mixer.forward(u, ctx, cache, add_output_bias=False) if bias is not None else \
+            self.mixer.forward(u, ctx, cache)
+        terms = (a,) if self.ffn is None else (a, self.ffn.forward(u))
+        trace = ctx.extras.get("residual_trace")         # a list: the stream after every layer (a copy)
+        if trace is not None or not getattr(next_norm, "takes_pending_sum", False):
+            from ..kernels import ops
+            ops.add_rows(h, terms, bias)
+            if trace is not None:
+                trace.append(h.clone())
+            return h, None
+        return h, PendingSum(terms, bias)

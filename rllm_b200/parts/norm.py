@@ -12,7 +12,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..kernels import ops
-from .base import Norm, RowSumsq, ScaledRows
+from .base import Norm, PendingSum, RowSumsq, ScaledRows
 from .registry import register_part
 from .spec import PartSpec, TensorSpec
 
@@ -103,4 +103,59 @@ class DynamicTanh(Norm):
     def gather_forward(self, x, delta, rows, act_dtype):
         out = torch.empty((rows.numel(), x.shape[1]), dtype=act_dtype, device=x.device)
         ops.dyt(x, self.alpha, self.weight, self.shift, out, delta=delta, rows=rows)
+        return out
+
+
+@register_part("norm", "layernorm")
+class LayerNorm(Norm):
+    """y = (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * w + b, row by row in float32: the norm with
+    statistics of both orders, a weight and a bias.  It completes the stream in the same kernel from up to
+    two sublayer results and a bias on every row (``PendingSum``), which is what a layer whose mixer and
+    feed-forward read the same normalised input leaves behind.
+
+    params: size, eps, name, bias_name (tensor names below the prefix)."""
+    graph_safe = True
+    takes_pending_sum = True
+
+    def __init__(self, spec: PartSpec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        self.size = int(spec["size"])
+        self.eps = float(spec["eps"])
+        self.name = prefix + str(spec["name"])
+        self.bias_name = prefix + str(spec["bias_name"])
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(self.name, (self.size,), role="vector", init=("one_plus_normal", 0.1)),
+                TensorSpec(self.bias_name, (self.size,), role="vector", init=("normal", 0.1))]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        # two vectors of the model's width: kept in float32 whatever the run's dtype
+        self.weight = tensors[self.name].float().contiguous()
+        self.bias = tensors[self.bias_name].float().contiguous()
+
+    @staticmethod
+    def _terms(delta):
+        if delta is None:
+            return (), None
+        if isinstance(delta, PendingSum):
+            return tuple(delta.terms), delta.bias
+        return (delta,), None
+
+    def forward(self, x: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:
+        out = torch.empty(x.shape, dtype=act_dtype, device=x.device)
+        ops.layernorm(x, self.weight, self.bias, self.eps, out)
+        return out
+
+    def add_forward(self, x: torch.Tensor, delta) -> torch.Tensor:
+        terms, row_bias = self._terms(delta)
+        out = torch.empty(x.shape, dtype=terms[0].dtype, device=x.device)
+        ops.layernorm(x, self.weight, self.bias, self.eps, out, deltas=terms, row_bias=row_bias, writeback=True)
+        return out
+
+    def gather_forward(self, x, delta, rows, act_dtype):
+        terms, row_bias = self._terms(delta)
+        out = torch.empty((rows.numel(), x.shape[1]), dtype=act_dtype, device=x.device)
+        ops.layernorm(x, self.weight, self.bias, self.eps, out, deltas=terms, row_bias=row_bias, rows=rows)
         return out

@@ -7,6 +7,14 @@ orig/high_freq_factor: kept; longer than orig/low_freq_factor: divided by
 declares the scaling struct, crates/rllm-core/src/config.rs:25-31, and never
 fills it, crates/rllm-model/src/hf_config.rs:68.)
 
+A second rescaling rule, ``scaling`` with ``kind`` "yarn" (factor, original,
+fast, slow): with turns(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta),
+the pair index at which a frequency makes t turns over ``original`` positions,
+lo = max(floor(turns(fast)), 0) and hi = min(ceil(turns(slow)), rotary_dim - 1),
+pair i gets the blend r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) of the
+slowed frequency: f_i / factor * r_i + f_i * (1 - r_i); and cosine and sine
+are both multiplied by 0.1 ln(factor) + 1 (``Rotary.magnitude``; 1 otherwise).
+
 No table over positions is stored: the kernel computes cos and sin of
 position * f_i in float64 per token, which is what the reference's table holds
 (rope.rs:24-28), for any position.
@@ -29,6 +37,19 @@ def rotary_frequencies(rotary_dim: int, theta: float, scaling: Optional[dict]) -
     if not scaling:
         return freqs
     factor = float(scaling["factor"])
+    if scaling.get("kind") == "yarn":
+        orig, theta = float(scaling["original"]), float(theta)
+
+        def turns(t: float) -> float:
+            return rotary_dim * math.log(orig / (2.0 * math.pi * t)) / (2.0 * math.log(theta))
+
+        lo = max(math.floor(turns(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(turns(float(scaling["slow"]))), rotary_dim - 1)
+        out = []
+        for i, f in enumerate(freqs):
+            r = min(1.0, max(0.0, (i - lo) / max(hi - lo, 0.001)))
+            out.append(f / factor * r + f * (1.0 - r))
+        return out
     low = float(scaling["low_freq_factor"])
     high = float(scaling["high_freq_factor"])
     orig = float(scaling["original_max_position_embeddings"])
@@ -66,6 +87,9 @@ class Rotary(PositionEncoding):
         scaling = p.get("scaling")
         self.scaling = dict(scaling) if scaling else None
         self.freqs = rotary_frequencies(self.rotary_dim, float(p["theta"]), self.scaling)
+        # what cosine and sine are multiplied by (the plain rotation and the llama3 rule: 1)
+        self.magnitude = 0.1 * math.log(float(self.scaling["factor"])) + 1.0 \
+            if self.scaling and self.scaling.get("kind") == "yarn" else 1.0
         self._table: Optional[torch.Tensor] = None
         self._ignored = [prefix + str(n) for n in (p.get("ignored_tensors") or ())]
 

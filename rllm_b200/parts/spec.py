@@ -121,25 +121,39 @@ class KVPagesNeed:
     ``window`` tokens, in pages.  ``values`` False: a token keeps ONE row of
     ``head_dim`` values per kv head that serves as key and as value (a latent);
     the storage then has no second buffer.  ``v_dim``: the size of a value row
-    where it is not a key row's (None: ``head_dim``)."""
+    where it is not a key row's (None: ``head_dim``).  ``keep_first``: beside
+    the window, the first that many tokens of a sequence stay (their pages are
+    never given back).  ``chunk``: a query needs only the keys of its own chunk
+    of that many positions, counted from position 0 (None: no such limit)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     values: bool = True
     v_dim: Optional[int] = None
+    keep_first: int = 0
+    chunk: Optional[int] = None
 
     @property
     def value_dim(self) -> int:
         return self.head_dim if self.v_dim is None else self.v_dim
 
+    @property
+    def span(self) -> Optional[int]:
+        """The most keys behind a query (itself included) that it can still need, the kept first tokens
+        aside; None: all of them.  Pages behind that are given back."""
+        spans = [int(x) for x in (self.window, self.chunk) if x is not None]
+        return min(spans) if spans else None
+
     def widened(self, other: "KVPagesNeed") -> Optional["KVPagesNeed"]:
-        """The need that keeps what both keep, if the rows are the same and only the windows differ."""
+        """The need that keeps what both keep, if the rows are the same and only what is visible differs."""
         if (self.num_kv_heads, self.head_dim, self.values, self.value_dim) != \
                 (other.num_kv_heads, other.head_dim, other.values, other.value_dim):
             return None
+        if (self.keep_first, self.chunk) != (other.keep_first, other.chunk):
+            return KVPagesNeed(self.num_kv_heads, self.head_dim, None, self.values, self.v_dim)   # every key
         w = None if self.window is None or other.window is None else max(self.window, other.window)
-        return KVPagesNeed(self.num_kv_heads, self.head_dim, w, self.values, self.v_dim)
+        return KVPagesNeed(self.num_kv_heads, self.head_dim, w, self.values, self.v_dim, self.keep_first, self.chunk)
 
 
 @dataclass(frozen=True)
