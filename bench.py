@@ -451,6 +451,31 @@ FEVOLORN_SIZES = {
 }
 
 
+def munupel(layers, width, heads, kv_heads, dim, window, keep, chunk, cap, ff, vocab):
+    """layers of the pattern [window with kept first tokens and sinks, chunked with capped scores and biases]:
+    parallel-residual layers of one layer norm, gated attention and a dense feed-forward."""
+    rot = {"base": 500000.0, "dims": dim // 2}
+    win = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+           "mask": {"size": window, "keep_first": keep}, "rot": rot}
+    chk = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": cap,
+           "mask": {"size": chunk},
+           "rot": dict(rot, scaling={"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0})}
+    return {"architecture": "Munupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "max_positions": 8192,
+            "layers": [{"type": "attention_2" if i % 2 == 0 else "attention", "mixer": win if i % 2 == 0 else chk,
+                        "mlp": {"kind": "dense", "ff": ff}} for i in range(layers)]}
+
+
+# Munupel beside the Llama (the closest design: grouped-query attention over pages, a SiLU-gated dense
+# feed-forward) of equal width, layers, heads, head size, feed-forward width and vocabulary.  The Llama sees
+# every earlier key; Munupel's layers see a window beside four kept tokens, or their chunk.
+MUNUPEL_SIZES = {
+    "w1024": dict(layers=4, width=1024, heads=16, kv_heads=4, dim=64, window=512, keep=4, chunk=1024, cap=30.0,
+                  ff=2048, vocab=32768),
+    "w2048": dict(layers=4, width=2048, heads=16, kv_heads=4, dim=128, window=1024, keep=4, chunk=1024, cap=30.0,
+                  ff=4096, vocab=32768),
+}
+
+
 def compare_designs(args):
     """Prefill and decode throughput of Fasulix at sizes that resemble a real model's layers (random weights)
     beside the Llama of equal size, through the same step function; and, from one eager prefill step and one
@@ -474,14 +499,32 @@ def compare_designs(args):
         """(flops, bytes) a call has to do at the least, from its arguments; None: not modelled."""
         S, ctx, Tn = shape["seqs"], shape["ctx"], shape["tokens"]
         pairs = sum(min(p + 1, shape.get("window") or p + 1) for p in range(ctx - Tn // S, ctx)) * S
+
+        def seen(window, keep, chunk):
+            """(query-key pairs, keys that have to be read) of the step under a mask."""
+            def lo(p):
+                a = max(0, p - window + 1) if window else 0
+                return max(a, p // chunk * chunk) if chunk else a
+            first = ctx - Tn // S
+            vis = sum(p + 1 - lo(p) + min(keep if window else 0, lo(p)) for p in range(first, ctx)) * S
+            return vis, S * (ctx - lo(first) + min(keep if window else 0, lo(first)))
         if name == "latent_attention_mma":
             q, heads, dk, dv, window = a[0], a[8], a[9], a[10], a[11]
             vis = sum(min(p + 1, window or p + 1) for p in range(ctx - Tn // S, ctx)) * S
             keys = S * min(ctx, (window or ctx) + Tn // S)
             return 2.0 * (dk + dv) * heads * vis, 2.0 * (keys * dk + q.numel() + a[1].numel())
         if name in ("attention_prefill_tcgen05", "attention_prefill_bf16", "attention_decode_bf16"):
-            nq, nkv, d = (a[11], a[12], a[13]) if name != "attention_decode_bf16" else (a[9], a[10], a[11])
-            return 4.0 * d * nq * pairs, 2.0 * (2 * S * ctx * nkv * d + 2 * Tn * nq * d)
+            nq, nkv, d, window = (a[11], a[12], a[13], a[14]) if name != "attention_decode_bf16" else \
+                (a[9], a[10], a[11], a[12])
+            vis, keys = seen(window, kw.get("keep_first", 0), kw.get("chunk", 0))
+            return 4.0 * d * nq * vis, 2.0 * (2 * keys * nkv * d + 2 * Tn * nq * d)
+        if name == "layernorm":
+            extra = len(kw.get("deltas", ())) * 2.0 + (4.0 if kw.get("writeback") else 0.0)
+            return 0.0, a[4].numel() * (4.0 + 2.0 + extra)
+        if name == "add_rows":
+            return 0.0, a[0].numel() * (8.0 + 2.0 * len(a[1]))
+        if name == "add_row_bias":
+            return 0.0, a[0].numel() * 4.0
         if name == "moe_experts":
             h, ids, wgu = a[0], a[1], a[2]
             E, F2, H = wgu.shape
@@ -511,8 +554,7 @@ def compare_designs(args):
             return 0.0, 6.0 * a[0].numel()
         if name == "attention_simt_kv":
             dk, dv, nq, nkv, window = a[3].shape[3], a[4].shape[3], a[8], a[9], a[10]
-            vis = sum(min(p + 1, window or p + 1) for p in range(ctx - Tn // S, ctx)) * S
-            keys = S * min(ctx, (window or ctx) + Tn // S)
+            vis, keys = seen(window, kw.get("keep_first", 0), kw.get("chunk", 0))
             return 2.0 * (dk + dv) * nq * vis, 2.0 * (keys * nkv * (dk + dv) + Tn * nq * (dk + dv))
         if name == "gated_postnorm_add":
             return 0.0, 8.0 * a[0].numel() + 2.0 * (a[2].numel() + 2 * a[3].numel())
@@ -538,7 +580,7 @@ def compare_designs(args):
             "silu_mul", "latent_prep", "latent_q_rot", "rope_kv_write", "gemm_small_m", "moe_choose", "gemm_small_m_residual",
             "gemm_small_m_rstd", "gemm_tcgen05", "embedding", "lightning_scan", "selective_scan", "causal_conv",
             "streams_read", "streams_write", "head_norm_kv_write", "attention_simt_kv", "rms_mean2", "gated_rmsnorm",
-            "act_mul", "moe_choose_sigmoid", "weighted_slot_sum")]
+            "act_mul", "moe_choose_sigmoid", "weighted_slot_sum", "layernorm", "add_rows", "add_row_bias")]
         saved, log = {}, []
 
         def wrap(name, fn):
@@ -661,7 +703,10 @@ def compare_designs(args):
         row = {"size": name}
         if args.design == "fevolorn":
             row["fevolorn"] = measure("fevolorn", fevolorn(**FEVOLORN_SIZES[name]))
-        row["fasulix"] = measure("fasulix", fasulix(**fx))
+        if args.design == "munupel":
+            row["munupel"] = measure("munupel", munupel(**MUNUPEL_SIZES[name]))
+        else:
+            row["fasulix"] = measure("fasulix", fasulix(**fx))
         cfg = llama(ll["layers"], ll["hidden"], ll["heads"], ll["kv_heads"], ll["head_dim"], ll["inter"], 32.0, True)
         cfg["vocab_size"] = fx["vocab"]
         row["llama"] = measure("llama", cfg)
@@ -690,7 +735,7 @@ def main():
     ap.add_argument("--no-standin", action="store_true", help="skip the library-operator stand-in")
     ap.add_argument("--settle-steps", type=int, default=SETTLE_STEPS,
                     help="untimed decode steps of a device-timed point before its warm-up steps (0 for a short capture under a profiler)")
-    ap.add_argument("--design", default=None, choices=["fasulix", "fevolorn"],
+    ap.add_argument("--design", default=None, choices=["fasulix", "fevolorn", "munupel"],
                     help="instead of the default workload: this design beside the Llama of equal size (prefill and "
                          "decode throughput, kernels against their rooflines)")
     ap.add_argument("--design-size", default=None, help="only this entry of the design comparison's sizes")

@@ -27,6 +27,22 @@
 #include <stdlib.h>
 #include <math.h>
 
+// Options beyond that contract (the kernels' OPT forms; each off at 0 / null), as in attention_simt.cu:
+//   keep_first  with a window: keys 0 .. keep_first - 1 stay visible however far back they lie;
+//   chunk       the query sees only keys of its own chunk, floor(j / chunk) == floor(p / chunk);
+//   softcap     score <- softcap * tanh(score / softcap) after the scaling;
+//   sinks       float32 [nq]: exp(sinks[h]) joins the softmax's denominator (no key, no value, unscaled);
+//   gate        a row of gate pre-activations per token: the result is multiplied by sigmoid(gate[h])
+//               (gate_mode 1, one number a head) or sigmoid(gate[h * d + i]) (gate_mode 2, one an element).
+// The plain forms are compiled without any of it.
+struct AttnOpts {
+  int keep_first, chunk;
+  float softcap;
+  const float* sinks;
+  const bf16* gate;
+  int gate_stride, gate_mode;
+};
+
 #define BM 64          // rows per CTA (prefill)
 #define BN 64          // keys per tile
 #define NTHREADS 128
@@ -77,12 +93,13 @@ template <int D> __device__ __forceinline__ bf16* tile_ptr(bf16* base, int row, 
 // or -1 for keys outside [lo, hi) and for pages the sequence does not hold.
 // Called by `rows` threads (one key each); the caller synchronises before the
 // offsets are used.
+// (keep_hi > 0: keys 0 .. keep_hi - 1 are read as well)
 __device__ __forceinline__ void kv_row_offsets(long long* rowoff, const int* __restrict__ bt, int j0, int r,
                                                int lo, int hi, int kvh, int nkv, int page_size, int page_shift,
-                                               int num_pages, int D, int* err) {
+                                               int num_pages, int D, int* err, int keep_hi = 0) {
   const int j = j0 + r;
   long long off = -1;
-  if (j >= lo && j < hi) {
+  if ((j >= lo || j < keep_hi) && j < hi) {
     const int pi = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
     const int pr = page_shift >= 0 ? (j & (page_size - 1)) : (j - pi * page_size);
     const int page = bt[pi];
@@ -165,11 +182,24 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
-template <int DT, int NT>
+// OPT: keys below row_keep[h] are visible too; with cap_b > 0 a raw score s becomes cap_b * tanh(s * cap_a)
+// (cap_a = scale / cap, cap_b = cap * log2 e: the capped score in the log2 domain) and is not scaled again.
+template <int DT, int NT, bool OPT = false>
 __device__ __forceinline__ void softmax_tile(float (*s)[4], float (*o)[4], float* m, float* l, int j0,
                                              const int* row_lo, const int* row_hi, float scale_log2,
-                                             int lane) {
-  const bool whole = j0 >= row_lo[0] && j0 + NT * 8 <= row_hi[0] && j0 >= row_lo[1] && j0 + NT * 8 <= row_hi[1];
+                                             int lane, const int* row_keep = nullptr, float cap_a = 0.f,
+                                             float cap_b = 0.f) {
+  if (OPT && cap_b > 0.f) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) s[nt][e] = cap_b * tanhf(s[nt][e] * cap_a);
+    scale_log2 = 1.0f;
+  }
+  bool whole = j0 >= row_lo[0] && j0 + NT * 8 <= row_hi[0] && j0 >= row_lo[1] && j0 + NT * 8 <= row_hi[1];
+  if (OPT)
+    whole = j0 + NT * 8 <= row_hi[0] && j0 + NT * 8 <= row_hi[1] && (j0 >= row_lo[0] || j0 + NT * 8 <= row_keep[0]) &&
+            (j0 >= row_lo[1] || j0 + NT * 8 <= row_keep[1]);
   if (!__all_sync(0xffffffffu, whole)) {     // some key of this tile is masked for some row of the warp
     const int col0 = (lane & 3) * 2;
 #pragma unroll
@@ -178,7 +208,8 @@ __device__ __forceinline__ void softmax_tile(float (*s)[4], float (*o)[4], float
       for (int e = 0; e < 4; ++e) {
         const int hrow = e >> 1;
         const int j = j0 + nt * 8 + col0 + (e & 1);
-        if (!(j >= row_lo[hrow] && j < row_hi[hrow])) s[nt][e] = -INFINITY;
+        const bool kept = OPT && j < row_keep[hrow];
+        if (!((j >= row_lo[hrow] || kept) && j < row_hi[hrow])) s[nt][e] = -INFINITY;
       }
   }
   float mx[2] = {-INFINITY, -INFINITY};
@@ -228,14 +259,14 @@ __device__ __forceinline__ void softmax_tile(float (*s)[4], float (*o)[4], float
 // ---------------------------------------------------------------------------
 // prefill
 // ---------------------------------------------------------------------------
-template <int D>
+template <int D, bool OPT>
 __global__ void __launch_bounds__(NTHREADS, (D <= 64 ? 4 : 2))
 attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out,
                          const bf16* __restrict__ kcache, const bf16* __restrict__ vcache,
                          const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ q_start, const int* __restrict__ seq_lens, int seq_begin,
                          int seq_end, int nq, int nkv, int page_size, int num_pages, int window,
-                         float scale_log2, int* __restrict__ err) {
+                         float scale_log2, int* __restrict__ err, AttnOpts opt) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   bf16* sQ = (bf16*)smem_raw;          // [BM][D]
   bf16* sK = sQ + BM * D;              // 2 stages [BN][D]
@@ -279,26 +310,42 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   cp_async_commit();
 
   const int first_pos = pos0 + t0, last_pos = pos0 + t0 + ntok - 1;
-  const int kmin = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
+  // the oldest key of the recent range that a query at position p sees (it grows with p)
+  auto oldest = [&](int p) {
+    int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    if (OPT && opt.chunk > 0) lo = max(lo, p / opt.chunk * opt.chunk);
+    return lo;
+  };
+  const int kmin = oldest(first_pos);
   const int kend = last_pos + 1;
   const int tile_lo = kmin / BN, tile_hi = (kend + BN - 1) / BN;
+  // OPT: the kept first keys that lie ahead of kmin (for some row of the tile they may lie inside the recent
+  // range: the mask is a union), and the key tiles that hold them ahead of tile_lo: walked first
+  const int keep = (OPT && window > 0) ? opt.keep_first : 0;
+  const int keep_hi = OPT ? min(keep, kmin) : 0;
+  const int keep_tiles = OPT ? min((keep_hi + BN - 1) / BN, tile_lo) : 0;
+  const int n_tiles = keep_tiles + tile_hi - tile_lo;
+  auto tile_at = [&](int it) { return (OPT && it < keep_tiles) ? it : tile_lo + it - keep_tiles; };
+  const float cap_a = (OPT && opt.softcap > 0.f) ? scale_log2 * 0.6931471805599453f / opt.softcap : 0.f;
+  const float cap_b = (OPT && opt.softcap > 0.f) ? opt.softcap * 1.4426950408889634f : 0.f;
 
   // this thread's two rows
-  int row_lo[2], row_hi[2];
+  int row_lo[2], row_hi[2], row_keep[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = warp * 16 + (lane >> 2) + h * 8;
     const int tl = r / g;
+    row_keep[h] = keep;
     if (tl < ntok) {
       const int p = pos0 + t0 + tl;
       row_hi[h] = p + 1;
-      row_lo[h] = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+      row_lo[h] = oldest(p);
     } else {
       row_lo[h] = 0; row_hi[h] = 0;            // idle row: sees nothing
     }
   }
 
-  if (tid < BN) kv_row_offsets(sOff, bt, tile_lo * BN, tid, kmin, kend, kvh, nkv, page_size, page_shift, num_pages, D, err);
+  if (tid < BN) kv_row_offsets(sOff, bt, tile_at(0) * BN, tid, kmin, kend, kvh, nkv, page_size, page_shift, num_pages, D, err, keep_hi);
   __syncthreads();
   copy_kv_pair<D>(sK, sV, kcache, vcache, sOff, BN, tid, NTHREADS);
   cp_async_commit();
@@ -318,12 +365,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
   for (int nt = 0; nt < D / 8; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-  for (int kt = tile_lo; kt < tile_hi; ++kt) {
-    const int stage = (kt - tile_lo) & 1;
-    const bool more = kt + 1 < tile_hi;
+  for (int it = 0; it < n_tiles; ++it) {
+    const int kt = tile_at(it);
+    const int stage = it & 1;
+    const bool more = it + 1 < n_tiles;
     if (more && tid < BN)
-      kv_row_offsets(sOff + (stage ^ 1) * BN, bt, (kt + 1) * BN, tid, kmin, kend, kvh, nkv, page_size, page_shift,
-                     num_pages, D, err);
+      kv_row_offsets(sOff + (stage ^ 1) * BN, bt, tile_at(it + 1) * BN, tid, kmin, kend, kvh, nkv, page_size, page_shift,
+                     num_pages, D, err, keep_hi);
     cp_async_wait<0>();
     __syncthreads();       // this stage's K and V are in; the next stage's offsets are published
     if (more) {            // the other stage was last read before the barrier that ended the previous iteration
@@ -333,23 +381,39 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     }
     float sc[8][4];
     qk_tile<D, 8>(sc, qf, sK + stage * BN * D, lane);
-    softmax_tile<D / 8, 8>(sc, o, m, l, kt * BN, row_lo, row_hi, scale_log2, lane);
+    softmax_tile<D / 8, 8, OPT>(sc, o, m, l, kt * BN, row_lo, row_hi, scale_log2, lane, row_keep, cap_a, cap_b);
     pv_tile<D, 8>(o, sc, sV + stage * BN * D, lane);
     __syncthreads();
   }
 
-  // epilogue: O / l
+  // epilogue: O / l (OPT: the sink joins l first; the gate's sigmoid multiplies the result)
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = warp * 16 + (lane >> 2) + h * 8;
     const int tl = r / g, hl = r - tl * g;
     if (tl >= ntok) continue;
-    const float inv = l[h] > 0.f ? 1.0f / l[h] : 0.f;
-    bf16* orow = out + ((size_t)(qs + t0 + tl) * nq + kvh * g + hl) * D + (lane & 3) * 2;
+    const int head = kvh * g + hl;
+    float keepf = 1.f, lsum = l[h];
+    if (OPT && opt.sinks) {
+      const float sk = opt.sinks[head] * 1.4426950408889634f;
+      const float top = fmaxf(m[h], sk);
+      keepf = m[h] == -INFINITY ? 0.f : exp2f(m[h] - top);
+      lsum = lsum * keepf + exp2f(sk - top);
+    }
+    float inv = lsum > 0.f ? keepf / lsum : 0.f;
+    const size_t tok = (size_t)(qs + t0 + tl);
+    const bf16* grow = (OPT && opt.gate_mode) ? opt.gate + tok * opt.gate_stride : nullptr;
+    if (OPT && opt.gate_mode == 1) inv *= 1.0f / (1.0f + expf(-to_f32(grow[head])));
+    bf16* orow = out + (tok * nq + head) * D + (lane & 3) * 2;
 #pragma unroll
     for (int nt = 0; nt < D / 8; ++nt) {
-      __nv_bfloat162 v = __floats2bfloat162_rn(o[nt][h * 2] * inv, o[nt][h * 2 + 1] * inv);
-      *(__nv_bfloat162*)(orow + nt * 8) = v;
+      float a = o[nt][h * 2] * inv, b = o[nt][h * 2 + 1] * inv;
+      if (OPT && opt.gate_mode == 2) {
+        const bf16* gp = grow + (size_t)head * D + (lane & 3) * 2 + nt * 8;
+        a *= 1.0f / (1.0f + expf(-to_f32(gp[0])));
+        b *= 1.0f / (1.0f + expf(-to_f32(gp[1])));
+      }
+      *(__nv_bfloat162*)(orow + nt * 8) = __floats2bfloat162_rn(a, b);
     }
   }
 }
@@ -430,7 +494,9 @@ __device__ __forceinline__ void copy_kv_pages(bf16* tile_k, bf16* tile_v, const 
 
 // SMALL: the smaller chunks are an option (small_below > 0) and the grid is laid out for them; without it the
 // chunk size is a constant of the kernel, which then is the kernel it was (registers and all).
-template <int D, int STAGES, int TBN, bool SMALL>
+// OPT: the options of the head comment (the kept first keys are a second range of chunks, walked by the
+// CTAs that hold them and merged ahead of the recent ones).
+template <int D, int STAGES, int TBN, bool SMALL, bool OPT = false>
 __global__ void __launch_bounds__(128, (STAGES == 1 && D <= 64 ? 5 : 1))
 attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__ out,
                         bf16* __restrict__ kcache, bf16* __restrict__ vcache,
@@ -439,7 +505,7 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
                         int window, float scale_log2, int max_chunks, const double* __restrict__ inv_freq,
                         int rotary_dim, int write_kv, float* __restrict__ ws_o, float* __restrict__ ws_ml,
                         int* __restrict__ counters, int* __restrict__ err, int tail_from, int first_wave,
-                        int small_below) {
+                        int small_below, AttnOpts opt) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   unsigned char* mine = smem_raw + (size_t)warp * dec_warp_smem<D, STAGES, TBN>();
@@ -467,13 +533,17 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
   const int chunk = cta_x * (blockDim.x >> 5) + warp;
   const int len = seq_lens[s];
   const int pos = len - 1;
-  const int kmin = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  int kmin_ = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  if (OPT && opt.chunk > 0) kmin_ = max(kmin_, pos / opt.chunk * opt.chunk);
+  const int kmin = kmin_;
+  // OPT: keys 0 .. kept - 1 lie ahead of the recent range and are seen as well
+  const int kept = (OPT && window > 0) ? min(opt.keep_first, kmin) : 0;
   const int ck = (SMALL && (long long)gridDim.x * gridDim.y * ((len + CHUNK - 1) / CHUNK) < small_below) ? CHUNK_SMALL : CHUNK;   // (SMALL: x, y = kv heads, sequences)
   const int w0 = chunk * ck;
   const int nwarps = blockDim.x >> 5;
   {  // a CTA none of whose chunks holds a visible key has nothing to do
     const int first = cta_x * nwarps * ck;
-    if (first >= len || first + nwarps * ck <= kmin) {
+    if (first >= len || (first + nwarps * ck <= kmin && first >= kept)) {
       // It still waits for the kernel ahead (it has not yet, with write_kv): a CTA that exits counts as
       // having let the next kernel in, and that kernel may then assume that everything but this kernel is
       // complete.  These CTAs do no work, so the wait costs nothing.
@@ -481,14 +551,14 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
       return;
     }
   }
-  const bool active = w0 < len && w0 + ck > kmin;
+  const bool active = w0 < len && (w0 + ck > kmin || w0 < kept);
   const int* bt = block_table + (size_t)s * max_blocks;
   const int half = rotary_dim >> 1;
   bf16* qrow = qkv + (size_t)s * q_stride;
   // keys to read from the cache: with write_kv the token's own key comes from qkv, not from the cache
   const int read_hi = write_kv ? pos : len;
-  const int t_lo = active ? (kmin > w0 ? (kmin - w0) / TBN : 0) : 0;
-  const int t_hi = active ? min((ck / TBN), (len - w0 + TBN - 1) / TBN) : 0;
+  const int t_lo = active ? ((kmin > w0 && w0 >= kept) ? (kmin - w0) / TBN : 0) : 0;
+  const int t_hi = active ? min((ck / TBN), ((w0 + ck > kmin ? len : kept) - w0 + TBN - 1) / TBN) : 0;
 
   // where the chunk's keys lie: all block-table lookups at once
   if (active) {
@@ -497,7 +567,7 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
       if (i * 32 >= ck) break;
       const int j = w0 + i * 32 + lane;
       int row = -1;
-      if (j >= kmin && j < read_hi) {
+      if ((j >= kmin || j < kept) && j < read_hi) {
         const int pi = page_shift >= 0 ? (j >> page_shift) : (j / page_size);
         const int pr = page_shift >= 0 ? (j & (page_size - 1)) : (j - pi * page_size);
         const int page = bt[pi];
@@ -585,13 +655,16 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
 #pragma unroll
     for (int kk = 0; kk < D / 16; ++kk)
       ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], tile_ptr<D>(sQ, lane & 15, kk * 2 + (lane >> 4)));
-    int row_lo[2], row_hi[2];
+    int row_lo[2], row_hi[2], row_keep[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int r = (lane >> 2) + h * 8;
       row_lo[h] = kmin;
       row_hi[h] = r < g ? len : 0;
+      row_keep[h] = kept;
     }
+    const float cap_a = (OPT && opt.softcap > 0.f) ? scale_log2 * 0.6931471805599453f / opt.softcap : 0.f;
+    const float cap_b = (OPT && opt.softcap > 0.f) ? opt.softcap * 1.4426950408889634f : 0.f;
     for (int t = t_lo; t < t_hi; ++t) {
       bf16* sK = sW + ((t - t_lo) % STAGES) * 2 * TBN * D;
       bf16* sV = sK + TBN * D;
@@ -621,7 +694,7 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
       }
       float sc[TBN / 8][4];
       qk_tile<D, TBN / 8>(sc, qf, sK, lane);
-      softmax_tile<D / 8, TBN / 8>(sc, o, m, l, j0, row_lo, row_hi, scale_log2, lane);
+      softmax_tile<D / 8, TBN / 8, OPT>(sc, o, m, l, j0, row_lo, row_hi, scale_log2, lane, row_keep, cap_a, cap_b);
       pv_tile<D, TBN / 8>(o, sc, sV, lane);
       __syncwarp();                // every lane is through with this stage
       issue(t + STAGES);
@@ -668,7 +741,11 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
   const int ck_m = (SMALL && (long long)gridDim.x * gridDim.y * ((len + CHUNK - 1) / CHUNK) < small_below) ? CHUNK_SMALL : CHUNK;
   const int ch_lo = kmin / ck_m, ch_hi = (len + ck_m - 1) / ck_m;
   const int cta_lo = ch_lo / nwarps, cta_hi = (ch_hi - 1) / nwarps + 1;
-  const int ncta = cta_hi - cta_lo;
+  // OPT: the CTAs 0 .. cta_keep - 1 ahead of cta_lo hold kept keys; place n of the merge is CTA cta_at(n)
+  const int cta_keep = OPT ? min((kept + nwarps * ck_m - 1) / (nwarps * ck_m), cta_lo) : 0;
+  const int ncta = cta_keep + cta_hi - cta_lo;
+  const int n_lo = OPT ? 0 : cta_lo, n_hi = OPT ? ncta : cta_hi;
+  auto cta_at = [&](int n) { return OPT ? (n < cta_keep ? n : cta_lo + n - cta_keep) : n; };
   __shared__ int s_last;
   asm volatile("fence.acq_rel.gpu;" ::: "memory");
   __syncthreads();
@@ -692,7 +769,7 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
     const bool valid = item < items;
     const int h = item & 1, q4 = (item >> 1) % (D / 4), r = valid ? (item >> 1) / (D / 4) : 0;
     const size_t base = ((size_t)s * nq + kvh * g + r) * max_chunks;
-    const int c_begin = cta_lo + h * half_n, c_end = valid ? min(cta_hi, c_begin + half_n) : c_begin;
+    const int c_begin = n_lo + h * half_n, c_end = valid ? min(n_hi, c_begin + half_n) : c_begin;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     float ll = 0.f, mm = -INFINITY;
     for (int c0 = c_begin; c0 < c_end; c0 += 8) {
@@ -700,7 +777,7 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
       float2 ml[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        const int c = min(c0 + j, c_end - 1);
+        const int c = cta_at(min(c0 + j, c_end - 1));
         v[j] = __ldcg((const float4*)(ws_o + (base + c) * D + q4 * 4));
         ml[j] = __ldcg((const float2*)(ws_ml + (base + c) * 2));
       }
@@ -726,13 +803,28 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
     const float llo = __shfl_xor_sync(0xffffffffu, ll, 1);
     const float mmo = __shfl_xor_sync(0xffffffffu, mm, 1);
     if (valid && h == 0) {
-      const float top = fmaxf(mm, mmo);
+      const int head = kvh * g + r;
+      float top = fmaxf(mm, mmo);
+      const float sk = (OPT && opt.sinks) ? opt.sinks[head] * 1.4426950408889634f : -INFINITY;
+      if (OPT) top = fmaxf(top, sk);
       const float fa = mm == -INFINITY ? 0.f : exp2f(mm - top), fb = mmo == -INFINITY ? 0.f : exp2f(mmo - top);
-      const float lt = ll * fa + llo * fb;
-      const float inv = lt > 0.f ? 1.0f / lt : 0.f;
-      bf16* o = out + ((size_t)s * nq + kvh * g + r) * D + q4 * 4;
-      __nv_bfloat162 lo = __floats2bfloat162_rn((acc.x * fa + oth.x * fb) * inv, (acc.y * fa + oth.y * fb) * inv);
-      __nv_bfloat162 hi = __floats2bfloat162_rn((acc.z * fa + oth.z * fb) * inv, (acc.w * fa + oth.w * fb) * inv);
+      float lt = ll * fa + llo * fb;
+      if (OPT && opt.sinks) lt += exp2f(sk - top);
+      float inv = lt > 0.f ? 1.0f / lt : 0.f;
+      float g0 = 1.f, g1 = 1.f, g2 = 1.f, g3 = 1.f;
+      if (OPT && opt.gate_mode) {
+        const bf16* grow = opt.gate + (size_t)s * opt.gate_stride;
+        if (opt.gate_mode == 1) {
+          inv *= 1.0f / (1.0f + expf(-to_f32(grow[head])));
+        } else {
+          const bf16* gp = grow + (size_t)head * D + q4 * 4;
+          g0 = 1.0f / (1.0f + expf(-to_f32(gp[0]))); g1 = 1.0f / (1.0f + expf(-to_f32(gp[1])));
+          g2 = 1.0f / (1.0f + expf(-to_f32(gp[2]))); g3 = 1.0f / (1.0f + expf(-to_f32(gp[3])));
+        }
+      }
+      bf16* o = out + ((size_t)s * nq + head) * D + q4 * 4;
+      __nv_bfloat162 lo = __floats2bfloat162_rn((acc.x * fa + oth.x * fb) * inv * g0, (acc.y * fa + oth.y * fb) * inv * g1);
+      __nv_bfloat162 hi = __floats2bfloat162_rn((acc.z * fa + oth.z * fb) * inv * g2, (acc.w * fa + oth.w * fb) * inv * g3);
       uint2 w;
       w.x = *(unsigned*)&lo; w.y = *(unsigned*)&hi;
       *(uint2*)o = w;
@@ -750,44 +842,45 @@ static bool mma_supported(int nq, int nkv, int d) {
 }
 
 template <int D> static size_t prefill_smem() { return (size_t)(BM + 4 * BN) * D * sizeof(bf16) + 2 * BN * sizeof(long long); }
-template <int D>
+template <int D, bool OPT>
 static int launch_prefill(const bf16* q, int q_stride, bf16* out, const bf16* kc, const bf16* vc,
                           const int* bt, int max_blocks, const int* q_start, const int* seq_lens,
                           int seq_begin, int seq_end, int num_tokens, int nq, int nkv, int page_size,
-                          int num_pages, int window, float scale, int* err, cudaStream_t stream) {
+                          int num_pages, int window, float scale, int* err, cudaStream_t stream, AttnOpts opt) {
   const int g = nq / nkv;
   const int bq = BM / g;
   const int tiles = (num_tokens + bq - 1) / bq + (seq_end - seq_begin);
   const size_t smem = prefill_smem<D>();
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<D, OPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   if ((long long)tiles * nkv > 0x7fffffffLL) return RLLM_E_UNSUPPORTED;
   dim3 grid(tiles * nkv);
-  attention_prefill_kernel<D><<<grid, NTHREADS, smem, stream>>>(q, q_stride, out, kc, vc, bt, max_blocks, q_start,
-      seq_lens, seq_begin, seq_end, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err);
+  attention_prefill_kernel<D, OPT><<<grid, NTHREADS, smem, stream>>>(q, q_stride, out, kc, vc, bt, max_blocks, q_start,
+      seq_lens, seq_begin, seq_end, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err, opt);
   RLLM_LAUNCH_CHECK();
   return 0;
 }
 
 // Prefill: sequences seq_begin .. seq_end-1 of the step, whose query tokens are
 // rows q_start[s] .. q_start[s+1]-1 of q and out; num_tokens bounds their count.
-RLLM_EXPORT int rllm_attention_prefill_bf16(const void* q, int q_stride, void* out, const void* kcache,
-                                            const void* vcache, const int* block_table, int max_blocks,
-                                            const int* q_start, const int* seq_lens, int seq_begin,
-                                            int seq_end, int num_tokens, int nq, int nkv, int d, int page_size,
-                                            int num_pages, int window, float scale, int* err,
-                                            cudaStream_t stream) {
+template <bool OPT>
+static int prefill_bf16(const void* q, int q_stride, void* out, const void* kcache,
+                        const void* vcache, const int* block_table, int max_blocks,
+                        const int* q_start, const int* seq_lens, int seq_begin,
+                        int seq_end, int num_tokens, int nq, int nkv, int d, int page_size,
+                        int num_pages, int window, float scale, int* err,
+                        cudaStream_t stream, AttnOpts opt) {
   if (seq_end <= seq_begin || num_tokens <= 0) return 0;
   if (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || window < 0 || q_stride % 8 || !(scale > 0.f))
     return RLLM_E_BADARG;
   if (!mma_supported(nq, nkv, d) || nq / nkv > BM) return RLLM_E_UNSUPPORTED;
-#define RLLM_PREFILL(DD) return launch_prefill<DD>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)kcache, \
+#define RLLM_PREFILL(DD) return launch_prefill<DD, OPT>((const bf16*)q, q_stride, (bf16*)out, (const bf16*)kcache, \
       (const bf16*)vcache, block_table, max_blocks, q_start, seq_lens, seq_begin, seq_end, num_tokens, nq, nkv, \
-      page_size, num_pages, window, scale, err, stream)
+      page_size, num_pages, window, scale, err, stream, opt)
   switch (d) {
     case 16: RLLM_PREFILL(16);
     case 32: RLLM_PREFILL(32);
@@ -797,23 +890,56 @@ RLLM_EXPORT int rllm_attention_prefill_bf16(const void* q, int q_stride, void* o
   return RLLM_E_UNSUPPORTED;
 }
 
+RLLM_EXPORT int rllm_attention_prefill_bf16(const void* q, int q_stride, void* out, const void* kcache,
+                                            const void* vcache, const int* block_table, int max_blocks,
+                                            const int* q_start, const int* seq_lens, int seq_begin,
+                                            int seq_end, int num_tokens, int nq, int nkv, int d, int page_size,
+                                            int num_pages, int window, float scale, int* err,
+                                            cudaStream_t stream) {
+  return prefill_bf16<false>(q, q_stride, out, kcache, vcache, block_table, max_blocks, q_start, seq_lens, seq_begin,
+                             seq_end, num_tokens, nq, nkv, d, page_size, num_pages, window, scale, err, stream,
+                             AttnOpts{0, 0, 0.f, nullptr, nullptr, 0, 0});
+}
+
+static int check_opts(int window, int keep_first, int chunk, float softcap, const void* gate, int gate_stride,
+                      int gate_mode) {
+  if (keep_first < 0 || chunk < 0 || !(softcap >= 0.f) || gate_mode < 0 || gate_mode > 2 || (gate_mode && !gate) ||
+      (keep_first > 0 && window <= 0) || (gate_mode && gate_stride <= 0))
+    return RLLM_E_BADARG;
+  return 0;
+}
+
+// The same with the options of the head comment; gate [tokens, gate_stride], a row per row of q.
+RLLM_EXPORT int rllm_attention_prefill_bf16_opts(const void* q, int q_stride, void* out, const void* kcache,
+                                                 const void* vcache, const int* block_table, int max_blocks,
+                                                 const int* q_start, const int* seq_lens, int seq_begin,
+                                                 int seq_end, int num_tokens, int nq, int nkv, int d, int page_size,
+                                                 int num_pages, int window, float scale, int keep_first, int chunk,
+                                                 float softcap, const float* sinks, const void* gate, int gate_stride,
+                                                 int gate_mode, int* err, cudaStream_t stream) {
+  if (check_opts(window, keep_first, chunk, softcap, gate, gate_stride, gate_mode)) return RLLM_E_BADARG;
+  return prefill_bf16<true>(q, q_stride, out, kcache, vcache, block_table, max_blocks, q_start, seq_lens, seq_begin,
+                            seq_end, num_tokens, nq, nkv, d, page_size, num_pages, window, scale, err, stream,
+                            AttnOpts{keep_first, chunk, softcap, sinks, (const bf16*)gate, gate_stride, gate_mode});
+}
+
 // floats of workspace that a decode call with these sizes needs
 RLLM_EXPORT long long rllm_attention_decode_workspace(int num_seqs, int nq, int d, int max_seq_len) {
   const long long chunks = 2 * ((max_seq_len + CHUNK - 1) / CHUNK);     // (room for chunks of CHUNK_SMALL keys)
   return (long long)num_seqs * nq * chunks * (d + 2);
 }
 
-template <int D, int STAGES, int TBN, bool SMALL>
+template <int D, int STAGES, int TBN, bool SMALL, bool OPT>
 static int launch_decode_small(int warps, bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc, const int* bt,
                              int max_blocks, const int* seq_lens, int num_seqs, int nq, int nkv, int page_size,
                              int num_pages, int window, float scale, int max_chunks, const double* inv_freq,
                              int rotary_dim, int write_kv, float* ws, int* counters, int* err,
-                             cudaStream_t stream, int small_below) {
+                             cudaStream_t stream, int small_below, AttnOpts opt) {
   if (SMALL) max_chunks *= CHUNK / CHUNK_SMALL;      // the grid and the workspace's stride: room for the smaller chunks
   const size_t smem = (size_t)warps * dec_warp_smem<D, STAGES, TBN>();
   static size_t configured = 0;
   if (smem > configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, STAGES, TBN, SMALL>,
+    cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<D, STAGES, TBN, SMALL, OPT>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     configured = smem;
@@ -823,52 +949,55 @@ static int launch_decode_small(int warps, bf16* qkv, int q_stride, bf16* out, bf
   const unsigned per_seq = (unsigned)((max_chunks + warps - 1) / warps);
   dim3 grid = SMALL ? dim3(nkv, num_seqs, per_seq) : dim3(per_seq, nkv, num_seqs);
   static int resident[5];        // by number of warps
-  if (!resident[warps]) resident[warps] = rllm_resident_ctas(attention_decode_kernel<D, STAGES, TBN, SMALL>, 32 * warps, smem) + 1;
+  if (!resident[warps]) resident[warps] = rllm_resident_ctas(attention_decode_kernel<D, STAGES, TBN, SMALL, OPT>, 32 * warps, smem) + 1;
   const long long ctas = (long long)grid.x * grid.y * grid.z;
   const int tail_from = (int)(ctas > resident[warps] - 1 ? ctas - (resident[warps] - 1) : 0);
-  cudaError_t e = rllm_launch_pdl(attention_decode_kernel<D, STAGES, TBN, SMALL>, grid, dim3(32 * warps), smem, stream, qkv,
+  cudaError_t e = rllm_launch_pdl(attention_decode_kernel<D, STAGES, TBN, SMALL, OPT>, grid, dim3(32 * warps), smem, stream, qkv,
       q_stride, out, kc, vc, bt, max_blocks, seq_lens, nq, nkv, page_size, num_pages, window,
       scale * 1.4426950408889634f, max_chunks, inv_freq, rotary_dim, write_kv, ws_o, ws_ml, counters, err, tail_from,
-      resident[warps] - 1, small_below);
+      resident[warps] - 1, small_below, opt);
   return (int)e;
 }
 
-template <int D, int STAGES, int TBN>
+template <int D, int STAGES, int TBN, bool OPT>
 static int launch_decode_cfg(int warps, bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc, const int* bt,
                              int max_blocks, const int* seq_lens, int num_seqs, int nq, int nkv, int page_size,
                              int num_pages, int window, float scale, int max_chunks, const double* inv_freq,
                              int rotary_dim, int write_kv, float* ws, int* counters, int* err,
-                             cudaStream_t stream, int small_below) {
+                             cudaStream_t stream, int small_below, AttnOpts opt) {
 #define RLLM_DEC_CFG_ARGS warps, qkv, q_stride, out, kc, vc, bt, max_blocks, seq_lens, num_seqs, nq, nkv, page_size, num_pages, \
-      window, scale, max_chunks, inv_freq, rotary_dim, write_kv, ws, counters, err, stream, small_below
-  if (small_below) return launch_decode_small<D, STAGES, TBN, true>(RLLM_DEC_CFG_ARGS);
-  return launch_decode_small<D, STAGES, TBN, false>(RLLM_DEC_CFG_ARGS);
+      window, scale, max_chunks, inv_freq, rotary_dim, write_kv, ws, counters, err, stream, small_below, opt
+  if constexpr (!OPT) {                            // (the smaller chunks are an option of the plain form only)
+    if (small_below) return launch_decode_small<D, STAGES, TBN, true, false>(RLLM_DEC_CFG_ARGS);
+  }
+  return launch_decode_small<D, STAGES, TBN, false, OPT>(RLLM_DEC_CFG_ARGS);
 }
 
 // Four warps a CTA.  With many chunks in all, one stage a warp, so that as many warps as possible are
 // resident per SM and hide each other's loads (measured best at batch 8 and 64, for heads of 64 and of 128:
 // 34.8 and 202 us at head size 128 against 49 and 298 us for two warps with three stages); with few chunks,
 // two stages a warp (best at batch 1).  The choice changes no result.
-template <int D>
+template <int D, bool OPT>
 static int launch_decode(bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc, const int* bt, int max_blocks,
                          const int* seq_lens, int num_seqs, int nq, int nkv, int page_size, int num_pages,
                          int window, float scale, int max_chunks, const double* inv_freq, int rotary_dim,
-                         int write_kv, float* ws, int* counters, int* err, cudaStream_t stream, bool allow_small) {
+                         int write_kv, float* ws, int* counters, int* err, cudaStream_t stream, bool allow_small,
+                         AttnOpts opt) {
   const long long total = (long long)max_chunks * nkv * num_seqs;
   // chunks of 64 keys are an option where even the longest sequences allowed would not make the work large
   // (the kernel decides sequence by sequence, by the sequence's own length)
-  const int small_below = (allow_small && total < 4096) ? CHUNK_SMALL_BELOW : 0;
+  const int small_below = (!OPT && allow_small && total < 4096) ? CHUNK_SMALL_BELOW : 0;
 #define RLLM_DEC_ARGS qkv, q_stride, out, kc, vc, bt, max_blocks, seq_lens, num_seqs, nq, nkv, page_size, num_pages, \
-      window, scale, max_chunks, inv_freq, rotary_dim, write_kv, ws, counters, err, stream, small_below
+      window, scale, max_chunks, inv_freq, rotary_dim, write_kv, ws, counters, err, stream, small_below, opt
   // Heads of 128: a tile of 32 keys is 16 KB of K and V, and one stage a warp leaves the warp without loads
   // in flight while it multiplies; tiles of 16 keys in two stages keep them coming in the same shared memory
   // (batch 8 x 4,096 keys: 33.4 against 35.0 us; batch 32 x 2,096: 62.3 against 63.3 us; three CTAs an SM with
   // one stage of 16 keys and 168 registers: 41.2 and 61.6 us).
   if constexpr (D == 128) {
-    if (total >= 1024) return launch_decode_cfg<D, 2, 16>(4, RLLM_DEC_ARGS);
+    if (total >= 1024) return launch_decode_cfg<D, 2, 16, OPT>(4, RLLM_DEC_ARGS);
   }
-  if (total >= 1024) return launch_decode_cfg<D, 1, 32>(4, RLLM_DEC_ARGS);
-  return launch_decode_cfg<D, 2, 32>(4, RLLM_DEC_ARGS);
+  if (total >= 1024) return launch_decode_cfg<D, 1, 32, OPT>(4, RLLM_DEC_ARGS);
+  return launch_decode_cfg<D, 2, 32, OPT>(4, RLLM_DEC_ARGS);
 }
 
 // Decode: sequences 0 .. num_seqs-1 with one query token each.  Row s of qkv
@@ -883,12 +1012,13 @@ static int launch_decode(bf16* qkv, int q_stride, bf16* out, bf16* kc, bf16* vc,
 // these must be complete when that kernel starts, i.e. written by a kernel at least two launches ahead
 // (or by a copy); only qkv may come from the kernel directly ahead.  Without write_kv it waits first.
 // Every seq_lens[s] must be at least 1.
+template <bool OPT>
 static int decode_bf16(void* qkv, int q_stride, void* out, void* kcache, void* vcache,
                        const int* block_table, int max_blocks, const int* seq_lens,
                        int num_seqs, int max_seq_len, int nq, int nkv, int d, int page_size,
                        int num_pages, int window, float scale, const double* inv_freq,
                        int rotary_dim, int write_kv, float* workspace, int* counters,
-                       int* err, cudaStream_t stream, bool allow_small) {
+                       int* err, cudaStream_t stream, bool allow_small, AttnOpts opt) {
   if (num_seqs <= 0) return 0;
   if (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || window < 0 || q_stride % 8 || max_seq_len <= 0 ||
       !workspace || !counters || !(scale > 0.f) || rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1) || (rotary_dim && !inv_freq))
@@ -897,9 +1027,9 @@ static int decode_bf16(void* qkv, int q_stride, void* out, void* kcache, void* v
   const int max_splits = (max_seq_len + CHUNK - 1) / CHUNK;
   if (max_splits > 65535 * 4 || num_seqs > 65535) return RLLM_E_UNSUPPORTED;
   if ((long long)num_pages * nkv * page_size > 0x7fffffffLL) return RLLM_E_UNSUPPORTED;   // cache rows are counted in an int
-#define RLLM_DECODE(DD) return launch_decode<DD>((bf16*)qkv, q_stride, (bf16*)out, (bf16*)kcache, (bf16*)vcache, \
+#define RLLM_DECODE(DD) return launch_decode<DD, OPT>((bf16*)qkv, q_stride, (bf16*)out, (bf16*)kcache, (bf16*)vcache, \
       block_table, max_blocks, seq_lens, num_seqs, nq, nkv, page_size, num_pages, window, scale, max_splits, \
-      inv_freq, rotary_dim, write_kv, workspace, counters, err, stream, allow_small)
+      inv_freq, rotary_dim, write_kv, workspace, counters, err, stream, allow_small, opt)
   switch (d) {
     case 16: RLLM_DECODE(16);
     case 32: RLLM_DECODE(32);
@@ -915,9 +1045,25 @@ RLLM_EXPORT int rllm_attention_decode_bf16(void* qkv, int q_stride, void* out, v
                                            int num_pages, int window, float scale, const double* inv_freq,
                                            int rotary_dim, int write_kv, float* workspace, int* counters,
                                            int* err, cudaStream_t stream) {
-  return decode_bf16(qkv, q_stride, out, kcache, vcache, block_table, max_blocks, seq_lens, num_seqs, max_seq_len, nq,
-                     nkv, d, page_size, num_pages, window, scale, inv_freq, rotary_dim, write_kv, workspace, counters,
-                     err, stream, true);
+  return decode_bf16<false>(qkv, q_stride, out, kcache, vcache, block_table, max_blocks, seq_lens, num_seqs, max_seq_len,
+                            nq, nkv, d, page_size, num_pages, window, scale, inv_freq, rotary_dim, write_kv, workspace,
+                            counters, err, stream, true, AttnOpts{0, 0, 0.f, nullptr, nullptr, 0, 0});
+}
+
+// The same with the options of the head comment, for tokens whose keys and values are in the cache already
+// (no rotation and no cache write here); gate [num_seqs, gate_stride], a row per sequence.
+RLLM_EXPORT int rllm_attention_decode_bf16_opts(void* q, int q_stride, void* out, void* kcache, void* vcache,
+                                                const int* block_table, int max_blocks, const int* seq_lens,
+                                                int num_seqs, int max_seq_len, int nq, int nkv, int d, int page_size,
+                                                int num_pages, int window, float scale, int keep_first, int chunk,
+                                                float softcap, const float* sinks, const void* gate, int gate_stride,
+                                                int gate_mode, float* workspace, int* counters, int* err,
+                                                cudaStream_t stream) {
+  if (check_opts(window, keep_first, chunk, softcap, gate, gate_stride, gate_mode)) return RLLM_E_BADARG;
+  return decode_bf16<true>(q, q_stride, out, kcache, vcache, block_table, max_blocks, seq_lens, num_seqs, max_seq_len,
+                           nq, nkv, d, page_size, num_pages, window, scale, nullptr, 0, 0, workspace, counters, err,
+                           stream, false,
+                           AttnOpts{keep_first, chunk, softcap, sinks, (const bf16*)gate, gate_stride, gate_mode});
 }
 
 // ---------------------------------------------------------------------------
@@ -974,7 +1120,8 @@ RLLM_EXPORT int rllm_attention_decode_bf16_static(void* qkv, int q_stride, void*
   // the merge counters must start at zero; an earlier call that was cut short may have left them set
   cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)num_seqs * nkv * sizeof(int), stream);
   if (e != cudaSuccess) return (int)e;
-  return decode_bf16(qkv, q_stride, out, kcache, vcache, block_table, max_blocks, seq_lens, num_seqs,
-                     max_seq_len, nq, nkv, d, page_size, num_pages, window, scale, inv_freq,
-                     rotary_dim, write_kv, scratch, counters, err, stream, allow_small);
+  return decode_bf16<false>(qkv, q_stride, out, kcache, vcache, block_table, max_blocks, seq_lens, num_seqs,
+                            max_seq_len, nq, nkv, d, page_size, num_pages, window, scale, inv_freq,
+                            rotary_dim, write_kv, scratch, counters, err, stream, allow_small,
+                            AttnOpts{0, 0, 0.f, nullptr, nullptr, 0, 0});
 }

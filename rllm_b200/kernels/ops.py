@@ -468,11 +468,24 @@ def logit_mask(logits: torch.Tensor, allowed_start: Optional[torch.Tensor],
 def attention_prefill_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor,
                            vcache: torch.Tensor, block_table: torch.Tensor, q_start: torch.Tensor,
                            seq_lens: torch.Tensor, seq_begin: int, seq_end: int, num_tokens: int, nq: int,
-                           nkv: int, d: int, window: int, scale: float, err: torch.Tensor) -> None:
-    """Tensor-core attention of the prompt portions of sequences seq_begin .. seq_end-1."""
+                           nkv: int, d: int, window: int, scale: float, err: torch.Tensor, keep_first: int = 0,
+                           chunk: int = 0, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None,
+                           gate: Optional[torch.Tensor] = None, gate_per_head: bool = False) -> None:
+    """Tensor-core attention of the prompt portions of sequences seq_begin .. seq_end-1.  ``keep_first``,
+    ``chunk``, ``softcap``, ``sinks`` and ``gate`` as in ``attention_simt_kv`` (gate: a row per row of q)."""
     lib = build.load_library("attention_mma")
     _contig(out, "out"); _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
     assert q.dtype is torch.bfloat16 and kcache.dtype is torch.bfloat16 and out.dtype is torch.bfloat16
+    if keep_first or chunk or softcap or sinks is not None or gate is not None:
+        gate_mode = _attention_opts_asserts(sinks, gate, gate_per_head, nq, d)
+        _check(lib.rllm_attention_prefill_bf16_opts(
+            _ptr(q), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_table),
+            c_int(block_table.shape[1]), _ptr(q_start), _ptr(seq_lens), c_int(seq_begin), c_int(seq_end),
+            c_int(num_tokens), c_int(nq), c_int(nkv), c_int(d), c_int(kcache.shape[2]), c_int(kcache.shape[0]),
+            c_int(window), c_float(scale), c_int(keep_first), c_int(chunk), c_float(softcap), _ptr(sinks), _ptr(gate),
+            c_int(gate.stride(0) if gate is not None else 0), c_int(gate_mode), _ptr(err), _stream()),
+            "attention_prefill_bf16_opts")
+        return
     _check(lib.rllm_attention_prefill_bf16(_ptr(q), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache),
                                            _ptr(block_table), c_int(block_table.shape[1]), _ptr(q_start),
                                            _ptr(seq_lens), c_int(seq_begin), c_int(seq_end), c_int(num_tokens),
@@ -511,6 +524,16 @@ _decode_counters = {}
 _retired_counters = []          # buffers that grew out of use: captured graphs may still hold their address
 
 
+def _attention_opts_asserts(sinks, gate, gate_per_head: bool, nq: int, d: int) -> int:
+    """Checks of the tensor-core kernels' options; returns the kernels' gate mode."""
+    if sinks is not None:
+        assert sinks.dtype is torch.float32 and sinks.numel() == nq and sinks.is_contiguous()
+    if gate is None:
+        return 0
+    assert gate.dtype is torch.bfloat16 and gate.stride(1) == 1 and gate.shape[1] == (nq if gate_per_head else nq * d)
+    return 1 if gate_per_head else 2
+
+
 def _counters_for(device: torch.device, n: int) -> torch.Tensor:
     """Zeroed per-device counters of the decode kernel's split merge; the kernel
     leaves them zero, so one buffer serves every call (also under CUDA graphs).
@@ -533,14 +556,18 @@ def attention_decode_bf16(qkv: torch.Tensor, q_stride: int, out: torch.Tensor, k
                           num_seqs: int, max_seq_len: int, nq: int, nkv: int, d: int, window: int,
                           scale: float, err: torch.Tensor, workspace: Optional[torch.Tensor] = None,
                           inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0,
-                          write_kv: bool = False) -> None:
+                          write_kv: bool = False, keep_first: int = 0, chunk: int = 0, softcap: float = 0.0,
+                          sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                          gate_per_head: bool = False) -> None:
     """Split-KV tensor-core attention of sequences 0 .. num_seqs-1, one query token
     each: row s of ``qkv`` holds the token's q heads (and behind them its k and v
     heads if ``write_kv``), row s of ``out`` gets the result.  ``rotary_dim`` > 0
     rotates q (and the new k) in the kernel; ``write_kv`` stores the token's k and
     v into the cache in the kernel.  ``max_seq_len`` bounds every length.  The
     workspace (float32, ``attention_decode_workspace`` elements) holds the splits'
-    partial results; it is allocated here if not given."""
+    partial results; it is allocated here if not given.  ``keep_first``, ``chunk``, ``softcap``, ``sinks`` and
+    ``gate`` as in ``attention_simt_kv`` (gate: a row per sequence), for tokens that are rotated and in the
+    cache already (neither ``rotary_dim`` nor ``write_kv``)."""
     lib = build.load_library("attention_mma")
     _contig(out, "out"); _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
     assert qkv.dtype is torch.bfloat16 and kcache.dtype is torch.bfloat16 and out.dtype is torch.bfloat16
@@ -551,6 +578,16 @@ def attention_decode_bf16(qkv: torch.Tensor, q_stride: int, out: torch.Tensor, k
     if rotary_dim:
         assert inv_freq is not None and inv_freq.dtype is torch.float64 and inv_freq.numel() == rotary_dim // 2
     counters = _counters_for(qkv.device, num_seqs * nkv)
+    if keep_first or chunk or softcap or sinks is not None or gate is not None:
+        assert not rotary_dim and not write_kv
+        gate_mode = _attention_opts_asserts(sinks, gate, gate_per_head, nq, d)
+        _check(lib.rllm_attention_decode_bf16_opts(
+            _ptr(qkv), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_table),
+            c_int(block_table.shape[1]), _ptr(seq_lens), c_int(num_seqs), c_int(max_seq_len), c_int(nq), c_int(nkv),
+            c_int(d), c_int(kcache.shape[2]), c_int(kcache.shape[0]), c_int(window), c_float(scale), c_int(keep_first),
+            c_int(chunk), c_float(softcap), _ptr(sinks), _ptr(gate), c_int(gate.stride(0) if gate is not None else 0),
+            c_int(gate_mode), _ptr(workspace), _ptr(counters), _ptr(err), _stream()), "attention_decode_bf16_opts")
+        return
     _check(lib.rllm_attention_decode_bf16(_ptr(qkv), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache),
                                           _ptr(block_table), c_int(block_table.shape[1]), _ptr(seq_lens),
                                           c_int(num_seqs), c_int(max_seq_len), c_int(nq), c_int(nkv), c_int(d),

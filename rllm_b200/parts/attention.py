@@ -164,6 +164,11 @@ class PagedAttention(Mixer):
             # stacked [Wq; Wk; Wv]: one matrix product gives a token's q, k and v side by side
             # (with a gate: [Wq; Wk; Wv; Wg], and the gate's pre-activations lie behind the value heads)
             stack = [tensors[q], tensors[k], tensors[v]] + ([tensors[self.prefix + self.names["g"]]] if self.gate else [])
+            rows = sum(t.shape[0] for t in stack)
+            if self.gate and rows % 8:
+                # rows of zeros, so that a token's row of the product starts on a 16-byte boundary in bfloat16
+                # (the tensor-core attention fetches its queries 16 bytes at a time)
+                stack.append(stack[0].new_zeros((8 - rows % 8, self.hidden)))
             self.w_qkv = torch.cat(stack, dim=0).contiguous()
         self.w_o = tensors[o]
         if self.bias:
@@ -212,29 +217,30 @@ class PagedAttention(Mixer):
             qkv = q_pad
         out = torch.empty((T, self.nq * dv), dtype=qkv.dtype, device=qkv.device)
         window, stride = int(self.window or 0), qkv.shape[1]
-        if not self.masked and dv == d and d % 16 == 0 and ops.use_mma_attention(qkv.dtype, self.nq, self.nkv, d):
+        gate = None
+        if self.gate:
+            at = self.nq * self.d + self.nkv * (self.d + self.dv)
+            gate = qkv[:, at: at + self.gate_width]
+        opts = dict(keep_first=self.keep_first, chunk=self.chunk, softcap=self.softcap, sinks=self.sink, gate=gate,
+                    gate_per_head=self.gate == "head") if self.masked else {}
+        if dv == d and d % 16 == 0 and ops.use_mma_attention(qkv.dtype, self.nq, self.nkv, d):
             nd = ctx.num_decode
             if nd:
                 ops.attention_decode_bf16(qkv, stride, out, cache.k, cache.v, table, ctx.seq_lens, nd,
                                           max(ctx.seq_lens_host[:nd]), self.nq, self.nkv, d, window, self.scale,
-                                          ctx.err, write_kv=False)
+                                          ctx.err, write_kv=False, **opts)
             if T > nd:
-                if ops.use_tcgen05_attention(qkv.dtype, self.nq, self.nkv, d, cache.k.shape[2]):
+                if not self.masked and ops.use_tcgen05_attention(qkv.dtype, self.nq, self.nkv, d, cache.k.shape[2]):
                     ops.attention_prefill_tcgen05(qkv, stride, out, cache.k, cache.v, table, ctx.q_start,
                                                   ctx.seq_lens, nd, ctx.num_seqs, T - nd, self.nq, self.nkv, d,
                                                   window, self.scale, ctx.err)
                 else:
                     ops.attention_prefill_bf16(qkv, stride, out, cache.k, cache.v, table, ctx.q_start, ctx.seq_lens,
                                                nd, ctx.num_seqs, T - nd, self.nq, self.nkv, d, window,
-                                               self.scale, ctx.err)
+                                               self.scale, ctx.err, **opts)
             return out
-        gate = None
-        if self.gate:
-            at = self.nq * self.d + self.nkv * (self.d + self.dv)
-            gate = qkv[:, at: at + self.gate_width]
         ops.attention_simt_kv(qkv, stride, out, cache.k, cache.v, table, ctx.positions, ctx.token_seq, self.nq,
-                              self.nkv, window, self.scale, ctx.err, keep_first=self.keep_first, chunk=self.chunk,
-                              softcap=self.softcap, sinks=self.sink, gate=gate, gate_per_head=self.gate == "head")
+                              self.nkv, window, self.scale, ctx.err, **opts)
         return out
 
     def deferred_output_bias(self) -> Optional[torch.Tensor]:
