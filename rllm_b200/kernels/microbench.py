@@ -66,6 +66,31 @@ def time_graph_us(fn, iters: int) -> float:
     return e0.elapsed_time(e1) * 1e3 / iters
 
 
+def _mask_options(args, rows: int, nq: int, d: int):
+    """The attention kernels' options from the command line: (keyword arguments, a word for the report)."""
+    kw = {}
+    if args.keep_first:
+        kw["keep_first"] = args.keep_first
+    if args.chunk:
+        kw["chunk"] = args.chunk
+    if args.softcap:
+        kw["softcap"] = args.softcap
+    if args.sinks:
+        kw["sinks"] = torch.randn(nq, device=DEV)
+    if args.gate:
+        kw["gate"] = torch.randn(rows, nq if args.gate == "head" else nq * d, device=DEV).bfloat16()
+        kw["gate_per_head"] = args.gate == "head"
+    return kw, (" with " + ", ".join(sorted(k for k in kw if k != "gate_per_head")) if kw else "")
+
+
+def _seen(p: int, window: int, keep: int, chunk: int) -> int:
+    """Keys that the query at position p sees."""
+    lo = max(0, p - window + 1) if window else 0
+    if chunk:
+        lo = max(lo, p // chunk * chunk)
+    return p + 1 - lo + (min(keep, lo) if window else 0)
+
+
 def attention_decode(args) -> None:
     nq, nkv, d, page = args.heads, args.kv_heads, args.head_dim, args.page
     B, ctx = args.batch, args.context
@@ -81,12 +106,16 @@ def attention_decode(args) -> None:
     ws = torch.empty(ops.attention_decode_workspace(B, nq, d, ctx), device=DEV)
     scale = 1 / math.sqrt(d)
 
+    kw, word = _mask_options(args, B, nq, d)
+
     def run(i):
         k, v = caches[i % nc]
-        ops.attention_decode_bf16(q, nq * d, out, k, v, table, seq_lens, B, ctx, nq, nkv, d, 0, scale, err, ws)
+        ops.attention_decode_bf16(q, nq * d, out, k, v, table, seq_lens, B, ctx, nq, nkv, d, args.window, scale, err, ws,
+                                  **kw)
     us = time_graph_us(run, args.iters)
-    nbytes = B * ctx * nkv * d * 2 * 2
-    print(f"attention_decode batch {B} context {ctx}: {us:.1f} us, {nbytes / us / 1e3:.0f} GB/s of K and V")
+    nbytes = B * _seen(ctx - 1, args.window, args.keep_first, args.chunk) * nkv * d * 2 * 2
+    print(f"attention_decode batch {B} context {ctx} window {args.window}{word}: {us:.1f} us, "
+          f"{nbytes / us / 1e3:.0f} GB/s of visible K and V")
 
 
 def attention_prefill(args) -> None:
@@ -104,12 +133,17 @@ def attention_prefill(args) -> None:
     scale = 1 / math.sqrt(d)
 
     fn = ops.attention_prefill_tcgen05 if args.impl == "tcgen05" else ops.attention_prefill_bf16
+    kw, word = _mask_options(args, T, nq, d)
+    if kw and args.impl == "tcgen05":
+        print("the tcgen05 kernel has the window alone among the options", file=sys.stderr)
+        return
 
     def run(i):
-        fn(q, nq * d, out, k, v, table, q_start, seq_lens, 0, 1, T, nq, nkv, d, 0, scale, err)
+        fn(q, nq * d, out, k, v, table, q_start, seq_lens, 0, 1, T, nq, nkv, d, args.window, scale, err, **kw)
     us = time_us(run, args.iters)
-    flops = 4 * d * nq * T * (T + 1) // 2
-    print(f"attention_prefill ({args.impl}) tokens {T}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s (causal)")
+    flops = 4 * d * nq * sum(_seen(p, args.window, args.keep_first, args.chunk) for p in range(T))
+    print(f"attention_prefill ({args.impl}) tokens {T} window {args.window}{word}: {us:.1f} us, "
+          f"{flops / us / 1e6:.0f} TFLOP/s (visible pairs)")
     if int(err.item()):
         print(f"error word {int(err.item())}", file=sys.stderr)
 
@@ -306,7 +340,12 @@ def main(argv=None) -> int:
     p.add_argument("--page", type=int, default=16)
     p.add_argument("--kv-rank", type=int, default=512, help="latent_attention: values of a cached row")
     p.add_argument("--rot-dim", type=int, default=64, help="latent_attention: the rows' rotated key part")
-    p.add_argument("--window", type=int, default=0, help="latent_attention: keys a query sees (0: all)")
+    p.add_argument("--window", type=int, default=0, help="the attention kernels: keys a query sees (0: all)")
+    p.add_argument("--keep-first", type=int, default=0, help="attention_*: with a window, first keys that stay visible")
+    p.add_argument("--chunk", type=int, default=0, help="attention_*: a query sees the keys of its own chunk")
+    p.add_argument("--softcap", type=float, default=0.0, help="attention_*: the tanh cap of the scaled scores")
+    p.add_argument("--sinks", action="store_true", help="attention_*: one more term a head in the denominator")
+    p.add_argument("--gate", choices=["head", "element"], default=None, help="attention_*: a sigmoid gate on the result")
     p.add_argument("--v-dim", type=int, default=0, help="lightning_scan: a value head's size (0: --head-dim)")
     p.add_argument("--channels", type=int, default=4096, help="selective_scan: inner channels")
     p.add_argument("--state", type=int, default=16, help="selective_scan: states a channel")

@@ -131,6 +131,53 @@ def test_window_gives_pages_back_and_reuses_them():
     m.check()
 
 
+@pytest.mark.parametrize("window,keep,page,step", [(10, 3, 4, 3), (10, 9, 4, 1), (5, 20, 8, 7), (16, 1, 16, 2), (3, 4, 4, 30)])
+def test_a_window_keeps_the_pages_of_the_first_tokens(window, keep, page, step):
+    """The pages that hold the first ``keep`` tokens stay for ever; those between them and the window go back and
+    are used again, so a fixed pool serves a sequence of any length."""
+    kept = -(-keep // page)
+    pool = kept + -(-(window + step) // page) + 2
+    m = CacheManager([KVPagesNeed(1, 16, window, keep_first=keep)], page, pool, 2)
+    m.admit("a")
+    pos, first_pages = 0, None
+    while pos < 400:
+        assert m.ensure("a", pos, pos + step), pos
+        tb = m.table("a", 0)
+        first_needed = max(0, pos - window + 1) // page
+        for k, p in enumerate(tb):
+            assert (p >= 0) == (k < kept or k >= first_needed), (pos, k, tb)
+        if len(tb) >= kept:
+            first_pages = first_pages or tb[:kept]
+            assert tb[:kept] == first_pages                # the same pages all the time
+        pos += step
+    m.check()
+    m.free("a")
+    assert m.num_free_pages(0) == pool
+    # a request that starts far behind its window (a forked or re-admitted one) takes the kept pages too
+    m.admit("b")
+    assert m.pages_needed("b", 0, 5 * (window + keep + page))[0] > pool or m.ensure("b", 0, 5 * (window + keep + page))
+    m.check()
+
+
+@pytest.mark.parametrize("chunk,page,step", [(13, 4, 3), (16, 16, 1), (32, 8, 5), (1, 4, 2), (50, 16, 23)])
+def test_chunks_that_have_ended_give_their_pages_back(chunk, page, step):
+    """A group whose queries see their own chunk of positions only: as soon as the next query lies in a later
+    chunk, the pages wholly ahead of that chunk go back."""
+    pool = -(-(chunk + step) // page) + 2
+    m = CacheManager([KVPagesNeed(1, 16, None, chunk=chunk)], page, pool, 2)
+    m.admit("a")
+    pos, seen = 0, set()
+    while pos < 300:
+        assert m.ensure("a", pos, pos + step), pos
+        tb = m.table("a", 0)
+        first_needed = (pos // chunk * chunk) // page
+        assert all(p == -1 for p in tb[:first_needed]) and all(p >= 0 for p in tb[first_needed:]), (pos, tb)
+        seen.update(p for p in tb if p >= 0)
+        pos += step
+    assert len(seen) <= pool
+    m.check()
+
+
 def test_a_prompt_that_starts_behind_its_window_holds_no_early_pages():
     m = CacheManager([KVPagesNeed(1, 16, 8)], 4, 4, 1)
     m.admit("a")
