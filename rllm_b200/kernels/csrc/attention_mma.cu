@@ -176,6 +176,11 @@ __device__ __forceinline__ void pv_tile(float (*o)[4], const float (*p)[4], bf16
 // Online-softmax update of one warp's 16 x (8 NT) score tile.  Thread holds rows
 // r0 = lane/4 and r0 + 8; positions and key ranges per row are given.
 //   s: raw scores in, probabilities out;  m, l: running max (log2 domain) and sum.
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // rcp(+inf) = +0
+  return y;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // ex2(-inf) = +0
@@ -183,7 +188,8 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 // OPT: keys below row_keep[h] are visible too; with cap_b > 0 a raw score s becomes cap_b * tanh(s * cap_a)
-// (cap_a = scale / cap, cap_b = cap * log2 e: the capped score in the log2 domain) and is not scaled again.
+// (cap_a = scale / cap, cap_b = cap * log2 e: the capped score in the log2 domain) and is not scaled again;
+// tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1), two special-function operations.
 template <int DT, int NT, bool OPT = false>
 __device__ __forceinline__ void softmax_tile(float (*s)[4], float (*o)[4], float* m, float* l, int j0,
                                              const int* row_lo, const int* row_hi, float scale_log2,
@@ -193,7 +199,8 @@ __device__ __forceinline__ void softmax_tile(float (*s)[4], float (*o)[4], float
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) s[nt][e] = cap_b * tanhf(s[nt][e] * cap_a);
+      for (int e = 0; e < 4; ++e)
+        s[nt][e] = fmaf(-2.0f * cap_b, rcp_approx(ex2_approx(s[nt][e] * (cap_a * 2.8853900817779268f)) + 1.0f), cap_b);
     scale_log2 = 1.0f;
   }
   bool whole = j0 >= row_lo[0] && j0 + NT * 8 <= row_hi[0] && j0 >= row_lo[1] && j0 + NT * 8 <= row_hi[1];

@@ -30,6 +30,11 @@
 //              of S that each has already read (heads of 64: no column is spare).
 // Contract and tile alignment as in attention_mma.cu (key tiles at absolute
 // positions; a row's arithmetic does not depend on the batch).
+// The OPT form has the options of attention_mma.cu's head comment: kept first keys behind a window (the key
+// tiles that hold them are walked ahead of the recent ones, by all three roles alike), chunks (the chunk's
+// start joins the window's), a tanh cap on the scaled scores (two special-function operations a score), a
+// sink in the denominator and a sigmoid gate on the result (both in the epilogue).  The plain form is compiled
+// without any of it.
 // Every mbarrier wait is bounded (bit 16 of the error word, then wind-down).
 // No cluster, no multicast.
 #include "tcgen05.cuh"
@@ -48,6 +53,11 @@
 __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z, void* bar) {
   asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
                ::"r"(tg_smem(dst)), "l"((unsigned long long)map), "r"(x), "r"(y), "r"(z), "r"(tg_smem(bar)) : "memory");
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));   // rcp(+inf) = +0
+  return y;
 }
 __device__ __forceinline__ float at_ex2(float x) {
   float y;
@@ -127,16 +137,25 @@ __device__ __forceinline__ bool pair_exchange(unsigned t_mine, unsigned t_theirs
   return true;
 }
 
+struct AtOpts {
+  int keep_first, chunk;
+  float softcap;
+  const float* sinks;
+  const bf16* gate;
+  int gate_stride, gate_mode;
+};
+
 // Q, two stages of K and of V, barriers: two CTAs fit one SM
 template <int AT_D> constexpr int at_smem_bytes() { return (AT_D / 64) * 16384 + 2 * AT_STAGE + 2 * AT_STAGE + 512; }
 
-template <int AT_D>
+template <int AT_D, bool OPT>
 __global__ void __launch_bounds__(AT_THREADS, 2)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
                          const int* __restrict__ block_table, int max_blocks, const int* __restrict__ q_start,
                          const int* __restrict__ seq_lens, int seq_begin, int seq_end, int nq, int nkv,
-                         int page_size, int num_pages, int window, float scale_log2, int* __restrict__ err) {
+                         int page_size, int num_pages, int window, float scale_log2, int* __restrict__ err,
+                         AtOpts opt) {
   constexpr int AT_BN = 8192 / AT_D;              // keys a tile
   constexpr int DP = AT_D / 64;                   // panels of head dims (Q, K, V)
   constexpr int KPANEL = AT_BN * 128;             // bytes of a K or V panel: BN rows of 128 bytes
@@ -182,9 +201,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
   const int t0 = tile * bq;
   const int ntok = min(bq, qlen - t0);
   const int first_pos = pos0 + t0, last_pos = pos0 + t0 + ntok - 1;
-  const int kmin = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
+  // the oldest key of the recent range that a query at position p sees (it grows with p)
+  auto oldest = [&](int p) {
+    int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    if (OPT && opt.chunk > 0) lo = max(lo, p / opt.chunk * opt.chunk);
+    return lo;
+  };
+  const int kmin = oldest(first_pos);
   const int kend = last_pos + 1;
   const int tile_lo = kmin / AT_BN, tile_hi = (kend + AT_BN - 1) / AT_BN;
+  // OPT: the kept first keys ahead of kmin and the key tiles ahead of tile_lo that hold them: walked first
+  const int keep = (OPT && window > 0) ? opt.keep_first : 0;
+  const int keep_tiles = OPT ? min((min(keep, kmin) + AT_BN - 1) / AT_BN, tile_lo) : 0;
+  const int num_tiles = keep_tiles + tile_hi - tile_lo;
+  auto tile_at = [&](int it) { return (OPT && it < keep_tiles) ? it : tile_lo + it - keep_tiles; };
   const int* bt = block_table + (size_t)s * max_blocks;
 
   // stale rows of K and V (pages that are skipped) must hold finite numbers: clear the ring once
@@ -223,19 +253,19 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // pages of 16 keys the requests, not the bytes, bound how fast tiles come in.)
     const int boxes = (AT_BN / page_size) * DP;     // page_size divides BN; at most 8 boxes
     const int bpage = lane / DP, bpanel = lane % DP; // this lane's box: which page of the tile, which panel
-    const int ntiles = tile_hi - tile_lo;
+    const int ntiles = num_tiles;
     // The page of this lane's box in tile `it`: read from the block table a tile ahead of its use (the load
     // is on its way while the warp polls), checked when the tile's keys are asked for, and kept in shared
     // memory until the tile's values are asked for (K runs at most three tiles ahead of V).
     auto fetch = [&](int it) {
-      const int j = (tile_lo + it) * AT_BN + bpage * page_size;
+      const int j = tile_at(it) * AT_BN + bpage * page_size;
       return (lane < boxes && it < ntiles && j < kend) ? bt[j / page_size] : -2;      // -2: no box
     };
     auto checked = [&](int it, int raw) {
       if (raw == -2) return -1;
       if (raw < 0 || raw >= num_pages) {
-        const int j = (tile_lo + it) * AT_BN + bpage * page_size;
-        if (j + page_size > kmin && bpanel == 0) atomicOr(err, 4);   // a page with visible keys is missing
+        const int j = tile_at(it) * AT_BN + bpage * page_size;
+        if ((j + page_size > kmin || j < keep) && bpanel == 0) atomicOr(err, 4);   // a page with visible keys is missing
         return -1;
       }
       return raw;
@@ -284,7 +314,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(AT_BN >> 3) << 17) | ((unsigned)(AT_BM >> 4) << 24);
       // (all D dims in one instruction: for D = 128 the two panels of V are a leading-dimension step apart)
       const unsigned idesc_pv = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(AT_D >> 3) << 17) | ((unsigned)(AT_BM >> 4) << 24);
-      const int ntiles = tile_hi - tile_lo;
+      const int ntiles = num_tiles;
       const unsigned long long dq = umma_desc(sQ);
       // scores of the tile in stage st: D / 16 steps along the head dims, panel by panel
       auto scores = [&](int st) {
@@ -341,13 +371,17 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // rows behind the portion's last token compute like the others; their result is not stored
     const int pos = pos0 + t0 + tl;
     const int row_hi = pos + 1;
-    const int row_lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int row_lo = oldest(pos);
     // tiles all of whose keys every row sees need no mask
-    const int clear_lo = (window > 0 && pos0 + t0 + bq - window > 0) ? pos0 + t0 + bq - window : 0;
+    const int clear_lo = oldest(pos0 + t0 + bq - 1);
     const int clear_hi = first_pos + 1;
+    const bool capped = OPT && opt.softcap > 0.f;
+    // capped scores: cap * log2 e * tanh(s * scale / cap), tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1)
+    const float cap_a = capped ? scale_log2 * 2.0f / opt.softcap : 0.f, cap_b = capped ? opt.softcap * 1.4426950408889634f : 0.f;
+    const float sl2 = capped ? 1.0f : scale_log2;
     float m_ref = -INFINITY, l = 0.f;
     const unsigned lane_sel = (unsigned)(quarter * 32) << 16;
-    const int ntiles = tile_hi - tile_lo;
+    const int ntiles = num_tiles;
     constexpr int HC = AT_BN / 2;                    // keys a thread
     // Where the two threads of a row swap values: in spare columns behind P if the CTA's 256 columns leave
     // four (heads of 128); else in the score columns that each thread has read itself (its first two), and
@@ -357,7 +391,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const unsigned x_theirs = X_SPARE ? tmem_p + AT_BN / 2 + lane_sel + (half ^ 1) * 2 : tmem_s + lane_sel + (half ^ 1) * HC;
     bool ok = true;
     for (int it = 0; it < ntiles; ++it) {
-      const int j0 = (tile_lo + it) * AT_BN;
+      const int j0 = tile_at(it) * AT_BN;
       ok = __all_sync(0xffffffffu, mbar_wait(s_full, it & 1, err));
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -370,11 +404,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         __syncwarp();
         if (lane == 0) mbar_arrive(s_free);
       }
+      if (capped) {
+#pragma unroll
+        for (int j = 0; j < HC; ++j) sc[j] = fmaf(-2.0f * cap_b, rcp_approx(at_ex2(sc[j] * cap_a) + 1.0f), cap_b);
+      }
       if (!(j0 >= clear_lo && j0 + AT_BN <= clear_hi)) {
         const unsigned lo_rel = (unsigned)(row_lo - j0 - half * HC), span = (unsigned)(row_hi - row_lo);
+        const int keep_rel = min(keep, row_hi) - j0 - half * HC;        // OPT: keys below it are kept first keys
 #pragma unroll
         for (int j = 0; j < HC; ++j)
-          if (!((unsigned)j - lo_rel < span)) sc[j] = -INFINITY;
+          if (!((unsigned)j - lo_rel < span || (OPT && j < keep_rel))) sc[j] = -INFINITY;
       }
       float mx0 = fmaxf(sc[0], sc[1]), mx1 = fmaxf(sc[2], sc[3]), mx2 = fmaxf(sc[4], sc[5]), mx3 = fmaxf(sc[6], sc[7]);
 #pragma unroll
@@ -391,7 +430,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         __syncwarp();
         if (lane == 0) mbar_arrive(s_free);
       }
-      mx = fmaxf(mx, mx_other) * scale_log2;
+      mx = fmaxf(mx, mx_other) * sl2;
       // The reference point of the exponentials moves only when the max has grown by more than 2^8: until
       // then the old one serves (probabilities up to 256, the sum and the output scale alike), and the
       // output accumulated so far needs no rescaling.  The rule looks at this row's scores only.
@@ -404,7 +443,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       }
       const float m_safe = (m_ref == -INFINITY) ? 0.f : m_ref;
       unsigned pk[HC / 2];
-      const unsigned long long scale2 = at_pack2(scale_log2, scale_log2), shift2 = at_pack2(-m_safe, -m_safe);
+      const unsigned long long scale2 = at_pack2(sl2, sl2), shift2 = at_pack2(-m_safe, -m_safe);
       unsigned long long sum01 = at_pack2(0.f, 0.f), sum23 = sum01;
 #pragma unroll
       for (int j = 0; j < HC; j += 4) {
@@ -479,11 +518,23 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     // exchange was for tile ntiles-1, this one takes the other parity)
     float lother = 0.f;
     if (ok) ok = pair_exchange(x_mine + (ntiles & 1), x_theirs + (ntiles & 1), &xbar[quarter], ntiles, l, &lother, err);
-    const float lsum = half == 0 ? l + lother : lother + l;
+    float lsum = half == 0 ? l + lother : lother + l;
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
-      bf16* orow = out + ((size_t)(qs + t0 + tl) * nq + kvh * g + hl) * AT_D + half * (AT_D / 2);
+      const int head = kvh * g + hl;
+      float keepf = 1.f;
+      if (OPT && opt.sinks && live) {                  // the sink joins the denominator: exp(sink), against the reference m_ref
+        const float sk = opt.sinks[head] * 1.4426950408889634f;
+        const float top = fmaxf(m_ref, sk);
+        keepf = m_ref == -INFINITY ? 0.f : exp2f(m_ref - top);
+        lsum = lsum * keepf + exp2f(sk - top);
+      }
+      float inv = lsum > 0.f ? keepf / lsum : 0.f;
+      const size_t tok = (size_t)(qs + t0 + (live ? tl : 0));
+      const bf16* grow = (OPT && opt.gate_mode) ? opt.gate + tok * opt.gate_stride : nullptr;
+      if (OPT && opt.gate_mode == 1) inv *= 1.0f / (1.0f + expf(-to_f32(grow[head < nq ? head : 0])));
+      const bf16* gel = (OPT && opt.gate_mode == 2 && live) ? grow + (size_t)head * AT_D + half * (AT_D / 2) : nullptr;
+      bf16* orow = out + ((size_t)(qs + t0 + tl) * nq + head) * AT_D + half * (AT_D / 2);
 #pragma unroll
       for (int c0 = 0; c0 < AT_D / 2; c0 += 32) {
         unsigned v[32];
@@ -495,8 +546,14 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             uint4 w;
             __nv_bfloat162* h = (__nv_bfloat162*)&w;
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-              h[q] = __floats2bfloat162_rn(__uint_as_float(v[c + 2 * q]) * inv, __uint_as_float(v[c + 2 * q + 1]) * inv);
+            for (int q = 0; q < 4; ++q) {
+              float a = __uint_as_float(v[c + 2 * q]) * inv, b = __uint_as_float(v[c + 2 * q + 1]) * inv;
+              if (OPT && gel) {
+                a *= 1.0f / (1.0f + expf(-to_f32(gel[c0 + c + 2 * q])));
+                b *= 1.0f / (1.0f + expf(-to_f32(gel[c0 + c + 2 * q + 1])));
+              }
+              h[q] = __floats2bfloat162_rn(a, b);
+            }
             *(uint4*)(orow + c0 + c) = w;
           }
         }
@@ -522,11 +579,11 @@ static int at_encode(CUtensorMap* map, int rank, const void* ptr, const cuuint64
   return r == CUDA_SUCCESS ? 0 : RLLM_E_BADARG;
 }
 
-template <int D>
+template <int D, bool OPT>
 static int at_launch(const void* q, int q_stride, int num_q_rows, void* out, const void* kcache, const void* vcache,
                      const int* block_table, int max_blocks, const int* q_start, const int* seq_lens, int seq_begin,
                      int seq_end, int num_tokens, int nq, int nkv, int page_size, int num_pages, int window,
-                     float scale, int* err, cudaStream_t stream) {
+                     float scale, int* err, cudaStream_t stream, AtOpts opt) {
   const int g = nq / nkv;
   CUtensorMap mq, mk, mv;
   {
@@ -548,7 +605,7 @@ static int at_launch(const void* q, int q_stride, int num_q_rows, void* out, con
   }
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, at_smem_bytes<D>());
+    cudaError_t e = cudaFuncSetAttribute(attention_tcgen05_kernel<D, OPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, at_smem_bytes<D>());
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
@@ -556,8 +613,8 @@ static int at_launch(const void* q, int q_stride, int num_q_rows, void* out, con
   const long long tiles = (num_tokens + bq - 1) / bq + (seq_end - seq_begin);
   if (tiles * nkv > 0x7fffffffLL) return RLLM_E_UNSUPPORTED;
   dim3 grid((unsigned)(tiles * nkv));
-  attention_tcgen05_kernel<D><<<grid, AT_THREADS, at_smem_bytes<D>(), stream>>>(mq, mk, mv, (bf16*)out, block_table, max_blocks,
-      q_start, seq_lens, seq_begin, seq_end, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err);
+  attention_tcgen05_kernel<D, OPT><<<grid, AT_THREADS, at_smem_bytes<D>(), stream>>>(mq, mk, mv, (bf16*)out, block_table, max_blocks,
+      q_start, seq_lens, seq_begin, seq_end, nq, nkv, page_size, num_pages, window, scale * 1.4426950408889634f, err, opt);
   RLLM_LAUNCH_CHECK();
   return 0;
 }
@@ -565,12 +622,13 @@ static int at_launch(const void* q, int q_stride, int num_q_rows, void* out, con
 // Sequences seq_begin .. seq_end-1 of the step; q rows q_start[s] .. q_start[s+1]-1 (num_q_rows rows of
 // q exist in all); head size 64 (pages of 16, 32, 64 or 128 keys) or 128 (pages of 16, 32 or 64); nq / nkv
 // up to 128 (a tile holds 128 / g tokens, rounded down).
-RLLM_EXPORT int rllm_attention_prefill_tcgen05(const void* q, int q_stride, int num_q_rows, void* out,
-                                               const void* kcache, const void* vcache, const int* block_table,
-                                               int max_blocks, const int* q_start, const int* seq_lens,
-                                               int seq_begin, int seq_end, int num_tokens, int nq, int nkv, int d,
-                                               int page_size, int num_pages, int window, float scale, int* err,
-                                               cudaStream_t stream) {
+template <bool OPT>
+static int at_prefill(const void* q, int q_stride, int num_q_rows, void* out,
+                      const void* kcache, const void* vcache, const int* block_table,
+                      int max_blocks, const int* q_start, const int* seq_lens,
+                      int seq_begin, int seq_end, int num_tokens, int nq, int nkv, int d,
+                      int page_size, int num_pages, int window, float scale, int* err,
+                      cudaStream_t stream, AtOpts opt) {
   if (seq_end <= seq_begin || num_tokens <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv || num_pages <= 0 || max_blocks <= 0 || window < 0 || !(scale > 0.f) || !err)
     return RLLM_E_BADARG;
@@ -580,8 +638,36 @@ RLLM_EXPORT int rllm_attention_prefill_tcgen05(const void* q, int q_stride, int 
       (((uintptr_t)q | (uintptr_t)kcache | (uintptr_t)vcache) & 15))
     return RLLM_E_UNSUPPORTED;
   if ((long long)num_pages * nkv * page_size > 0x7fffffffLL) return RLLM_E_UNSUPPORTED;   // cache rows are TMA coordinates
-#define AT_LAUNCH(DD) return at_launch<DD>(q, q_stride, num_q_rows, out, kcache, vcache, block_table, max_blocks, q_start, \
-      seq_lens, seq_begin, seq_end, num_tokens, nq, nkv, page_size, num_pages, window, scale, err, stream)
+#define AT_LAUNCH(DD) return at_launch<DD, OPT>(q, q_stride, num_q_rows, out, kcache, vcache, block_table, max_blocks, q_start, \
+      seq_lens, seq_begin, seq_end, num_tokens, nq, nkv, page_size, num_pages, window, scale, err, stream, opt)
   if (d == 64) AT_LAUNCH(64);
   AT_LAUNCH(128);
+}
+
+RLLM_EXPORT int rllm_attention_prefill_tcgen05(const void* q, int q_stride, int num_q_rows, void* out,
+                                               const void* kcache, const void* vcache, const int* block_table,
+                                               int max_blocks, const int* q_start, const int* seq_lens,
+                                               int seq_begin, int seq_end, int num_tokens, int nq, int nkv, int d,
+                                               int page_size, int num_pages, int window, float scale, int* err,
+                                               cudaStream_t stream) {
+  return at_prefill<false>(q, q_stride, num_q_rows, out, kcache, vcache, block_table, max_blocks, q_start, seq_lens,
+                           seq_begin, seq_end, num_tokens, nq, nkv, d, page_size, num_pages, window, scale, err, stream,
+                           AtOpts{0, 0, 0.f, nullptr, nullptr, 0, 0});
+}
+
+// The same with the options of the head comment; gate [num_q_rows, gate_stride], a row per row of q.
+RLLM_EXPORT int rllm_attention_prefill_tcgen05_opts(const void* q, int q_stride, int num_q_rows, void* out,
+                                                    const void* kcache, const void* vcache, const int* block_table,
+                                                    int max_blocks, const int* q_start, const int* seq_lens,
+                                                    int seq_begin, int seq_end, int num_tokens, int nq, int nkv, int d,
+                                                    int page_size, int num_pages, int window, float scale,
+                                                    int keep_first, int chunk, float softcap, const float* sinks,
+                                                    const void* gate, int gate_stride, int gate_mode, int* err,
+                                                    cudaStream_t stream) {
+  if (keep_first < 0 || chunk < 0 || !(softcap >= 0.f) || gate_mode < 0 || gate_mode > 2 || (gate_mode && !gate) ||
+      (keep_first > 0 && window <= 0) || (gate_mode && gate_stride <= 0))
+    return RLLM_E_BADARG;
+  return at_prefill<true>(q, q_stride, num_q_rows, out, kcache, vcache, block_table, max_blocks, q_start, seq_lens,
+                          seq_begin, seq_end, num_tokens, nq, nkv, d, page_size, num_pages, window, scale, err, stream,
+                          AtOpts{keep_first, chunk, softcap, sinks, (const bf16*)gate, gate_stride, gate_mode});
 }

@@ -134,9 +134,6 @@ def attention_prefill(args) -> None:
 
     fn = ops.attention_prefill_tcgen05 if args.impl == "tcgen05" else ops.attention_prefill_bf16
     kw, word = _mask_options(args, T, nq, d)
-    if kw and args.impl == "tcgen05":
-        print("the tcgen05 kernel has the window alone among the options", file=sys.stderr)
-        return
 
     def run(i):
         fn(q, nq * d, out, k, v, table, q_start, seq_lens, 0, 1, T, nq, nkv, d, args.window, scale, err, **kw)

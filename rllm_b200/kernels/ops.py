@@ -505,13 +505,25 @@ def attention_prefill_tcgen05_supported(nq: int, nkv: int, d: int, page_size: in
 def attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache: torch.Tensor,
                               vcache: torch.Tensor, block_table: torch.Tensor, q_start: torch.Tensor,
                               seq_lens: torch.Tensor, seq_begin: int, seq_end: int, num_tokens: int, nq: int,
-                              nkv: int, d: int, window: int, scale: float, err: torch.Tensor) -> None:
+                              nkv: int, d: int, window: int, scale: float, err: torch.Tensor, keep_first: int = 0,
+                              chunk: int = 0, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None,
+                              gate: Optional[torch.Tensor] = None, gate_per_head: bool = False) -> None:
     """Attention of the prompt portions of sequences seq_begin .. seq_end-1 on the
-    tcgen05 tensor cores (same contract as ``attention_prefill_bf16``; ``q`` is the
+    tcgen05 tensor cores (same contract and options as ``attention_prefill_bf16``; ``q`` is the
     first of ``q.shape[0]`` rows of ``q_stride`` elements)."""
     lib = build.load_library("attention_tcgen05")
     _contig(out, "out"); _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
     assert q.dtype is torch.bfloat16 and kcache.dtype is torch.bfloat16 and out.dtype is torch.bfloat16
+    if keep_first or chunk or softcap or sinks is not None or gate is not None:
+        gate_mode = _attention_opts_asserts(sinks, gate, gate_per_head, nq, d)
+        _check(lib.rllm_attention_prefill_tcgen05_opts(
+            _ptr(q), c_int(q_stride), c_int(q.shape[0]), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_table),
+            c_int(block_table.shape[1]), _ptr(q_start), _ptr(seq_lens), c_int(seq_begin), c_int(seq_end),
+            c_int(num_tokens), c_int(nq), c_int(nkv), c_int(d), c_int(kcache.shape[2]), c_int(kcache.shape[0]),
+            c_int(window), c_float(scale), c_int(keep_first), c_int(chunk), c_float(softcap), _ptr(sinks), _ptr(gate),
+            c_int(gate.stride(0) if gate is not None else 0), c_int(gate_mode), _ptr(err), _stream()),
+            "attention_prefill_tcgen05_opts")
+        return
     _check(lib.rllm_attention_prefill_tcgen05(_ptr(q), c_int(q_stride), c_int(q.shape[0]), _ptr(out), _ptr(kcache),
                                               _ptr(vcache), _ptr(block_table), c_int(block_table.shape[1]),
                                               _ptr(q_start), _ptr(seq_lens), c_int(seq_begin), c_int(seq_end),

@@ -230,10 +230,10 @@ class PagedAttention(Mixer):
                                           max(ctx.seq_lens_host[:nd]), self.nq, self.nkv, d, window, self.scale,
                                           ctx.err, write_kv=False, **opts)
             if T > nd:
-                if not self.masked and ops.use_tcgen05_attention(qkv.dtype, self.nq, self.nkv, d, cache.k.shape[2]):
+                if ops.use_tcgen05_attention(qkv.dtype, self.nq, self.nkv, d, cache.k.shape[2]):
                     ops.attention_prefill_tcgen05(qkv, stride, out, cache.k, cache.v, table, ctx.q_start,
                                                   ctx.seq_lens, nd, ctx.num_seqs, T - nd, self.nq, self.nkv, d,
-                                                  window, self.scale, ctx.err)
+                                                  window, self.scale, ctx.err, **opts)
                 else:
                     ops.attention_prefill_bf16(qkv, stride, out, cache.k, cache.v, table, ctx.q_start, ctx.seq_lens,
                                                nd, ctx.num_seqs, T - nd, self.nq, self.nkv, d, window,

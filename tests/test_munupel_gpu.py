@@ -143,7 +143,7 @@ def attention_case(dtype, path, nq, nkv, dk, dv, page, lens, news, scale, kind="
     """Sequences on shuffled pages; the last ``news[s]`` tokens of sequence s are this step's queries (every
     key, theirs included, is in the pages already).  ``path`` "simt": the CUDA-core kernel; "mma": the
     tensor-core kernels, the decode kernel for the sequences with one query (they come first) and the prompt
-    kernel for the rest.  Returns (got, want) [T, nq, dv]."""
+    kernel for the rest; "tcgen05": the same with the tcgen05 prompt kernel.  Returns (got, want) [T, nq, dv]."""
     from rllm_b200.kernels import ops
     g = torch.Generator().manual_seed(seed)
     S = len(lens)
@@ -200,7 +200,8 @@ def attention_case(dtype, path, nq, nkv, dk, dv, page, lens, news, scale, kind="
             ops.attention_decode_bf16(qg, qg.shape[1], out, kcd, vcd, table.cuda(), i32(lens), nd, max(lens[:nd]), nq,
                                       nkv, dk, window, scale, err, **opts)
         if S > nd:
-            ops.attention_prefill_bf16(qg, qg.shape[1], out, kcd, vcd, table.cuda(), q_start, i32(lens), nd, S, T - nd,
+            prompt = ops.attention_prefill_tcgen05 if path == "tcgen05" else ops.attention_prefill_bf16
+            prompt(qg, qg.shape[1], out, kcd, vcd, table.cuda(), q_start, i32(lens), nd, S, T - nd,
                                        nq, nkv, dk, window, scale, err, **opts)
     assert int(err.item()) == 0
     return out.view(T, nq, dv), torch.stack(want)
@@ -220,15 +221,24 @@ CASES = [  # nq, nkv, dk, dv, page, kind, size, keep, cap, sinks, gate
 ]
 
 
-@pytest.mark.parametrize("dtype,path", [("float32", "simt"), ("bfloat16", "simt"), ("bfloat16", "mma")])
+def takes(path, dk, dv, page):
+    if path == "mma":
+        return dk == dv and dk in (16, 32, 64, 128)
+    if path == "tcgen05":
+        return dk == dv and dk in (64, 128) and page in (16, 32, 64)
+    return True
+
+
+@pytest.mark.parametrize("dtype,path", [("float32", "simt"), ("bfloat16", "simt"), ("bfloat16", "mma"),
+                                        ("bfloat16", "tcgen05")])
 @pytest.mark.parametrize("case", CASES)
 def test_masks_cap_sink_and_gates_in_the_attention_kernels(dtype, path, case):
     """Two decoded tokens, a prompt portion behind a cached prefix and a whole short prompt in one step,
     keys on shuffled pages, against the formula in float64: a window beside kept first keys, chunks, a
     tanh cap on the scores, a sink in the denominator, a gate per head or per element."""
     nq, nkv, dk, dv, page, kind, size, keep, cap, sinks, gate = case
-    if path == "mma" and (dk != dv or dk not in (16, 32, 64, 128)):
-        pytest.skip("the tensor-core kernels take keys and values of one size: 16, 32, 64 or 128")
+    if not takes(path, dk, dv, page):
+        pytest.skip("the tensor-core kernels take keys and values of one size: 16, 32, 64 or 128 (tcgen05: 64, 128)")
     got, want = attention_case(dtype, path, nq, nkv, dk, dv, page, [141, 300, 83, 19], [1, 1, 50, 19], dk ** -0.5 * 3,
                                kind=kind, size=size, keep=keep, cap=cap, sinks=sinks, gate=gate, seed=nq + dk)
     assert rel(got, want) <= (3e-6 if dtype == "float32" else 2e-2)
@@ -244,17 +254,20 @@ def _one_loud_key(key_pos, n, new, path, **kw):
         k[key_pos].mul_(0.05)
         k[key_pos, :, 0] = 6.0
     dtype = "float32" if path == "simt" else "bfloat16"
-    return attention_case(dtype, path, 2, 1, 16, 16, kw.pop("page", 16), [n], [new], 4.0, boost=boost, **kw)
+    d = 64 if path == "tcgen05" else 16
+    return attention_case(dtype, path, 2, 1, d, d, kw.pop("page", 16), [n], [new], 4.0, boost=boost, **kw)
 
 
-@pytest.mark.parametrize("path", ["simt", "mma"])
-@pytest.mark.parametrize("new", [1, 30])
+@pytest.mark.parametrize("path", ["simt", "mma", "tcgen05"])
+@pytest.mark.parametrize("new", [1, 30, 200])
 @pytest.mark.parametrize("size,keep,page", [(5, 2, 16), (16, 1, 16), (17, 20, 4), (96, 6, 16), (64, 64, 16), (130, 3, 8)])
 def test_keys_at_the_edges_of_the_window_and_of_the_kept_first(path, new, size, keep, page):
     """The last query must see the oldest key of its window and not the one before it; it must see the last
     of the kept first keys and not the next one (which is far outside the window); as a decoded token and in
     a prompt portion, edges on and off page borders."""
-    n = 3 * size + keep + 70
+    if not takes(path, 64, 64, page):
+        pytest.skip("the tcgen05 kernel takes pages of 16, 32 or 64 keys")
+    n = 3 * size + keep + 270
     last = n - 1
     tol = 3e-6 if path == "simt" else 2e-2
     kw = dict(kind="window", size=size, keep=keep, page=page, seed=size)
@@ -267,12 +280,14 @@ def test_keys_at_the_edges_of_the_window_and_of_the_kept_first(path, new, size, 
         assert float((g1[-1].double().cpu() - w0[-1]).abs().max()) > 0.2
 
 
-@pytest.mark.parametrize("path", ["simt", "mma"])
-@pytest.mark.parametrize("new", [1, 30])
+@pytest.mark.parametrize("path", ["simt", "mma", "tcgen05"])
+@pytest.mark.parametrize("new", [1, 30, 200])
 @pytest.mark.parametrize("size,page", [(5, 16), (16, 16), (13, 4), (96, 16), (128, 16), (200, 8)])
 def test_keys_at_the_edges_of_a_chunk(path, new, size, page):
     """A query at the start, in the middle and at the end of its chunk sees the chunk's first key and not
     the last key of the chunk before; chunks are counted from the sequence's first position."""
+    if not takes(path, 64, 64, page):
+        pytest.skip("the tcgen05 kernel takes pages of 16, 32 or 64 keys")
     tol = 3e-6 if path == "simt" else 2e-2
     for n in (3 * size + 1, 3 * size + size // 2 + 1, 4 * size):
         if new > 1 and n <= new:
@@ -287,13 +302,14 @@ def test_keys_at_the_edges_of_a_chunk(path, new, size, page):
             assert float((g1[-1].double().cpu() - w0[-1]).abs().max()) > 0.2
 
 
-@pytest.mark.parametrize("path", ["simt", "mma"])
+@pytest.mark.parametrize("path", ["simt", "mma", "tcgen05"])
 def test_the_sink_takes_its_share_and_the_cap_holds_the_scores(path):
     """A sink as large as the largest score halves the result against no sink; a cap far below the scores
     makes the weights nearly equal."""
     dtype = "float32" if path == "simt" else "bfloat16"
     tol = 3e-6 if path == "simt" else 2e-2
-    args = (dtype, path, 4, 2, 32, 32, 16, [1, 77], [1, 40], 1.0)
+    d = 64 if path == "tcgen05" else 32
+    args = (dtype, path, 4, 2, d, d, 16, [1, 77], [1, 40], d ** -0.5)
     g1, w1 = attention_case(*args, sinks=True, seed=5)
     g0, w0 = attention_case(*args, sinks=False, seed=5)
     assert rel(g1, w1) <= tol and rel(g0, w0) <= tol
