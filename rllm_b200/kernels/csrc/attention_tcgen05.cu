@@ -532,7 +532,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       float inv = lsum > 0.f ? keepf / lsum : 0.f;
       const size_t tok = (size_t)(qs + t0 + (live ? tl : 0));
       const bf16* grow = (OPT && opt.gate_mode) ? opt.gate + tok * opt.gate_stride : nullptr;
-      if (OPT && opt.gate_mode == 1) inv *= 1.0f / (1.0f + expf(-to_f32(grow[head < nq ? head : 0])));
+      // sigmoid(x) = 1 / (1 + 2^(-x log2 e))
+      auto sigm = [](float x) { return rcp_approx(1.0f + at_ex2(x * -1.4426950408889634f)); };
+      if (OPT && opt.gate_mode == 1) inv *= sigm(to_f32(grow[head < nq ? head : 0]));
       const bf16* gel = (OPT && opt.gate_mode == 2 && live) ? grow + (size_t)head * AT_D + half * (AT_D / 2) : nullptr;
       bf16* orow = out + ((size_t)(qs + t0 + tl) * nq + head) * AT_D + half * (AT_D / 2);
 #pragma unroll
@@ -543,14 +545,22 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         if (live) {
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {
-            uint4 w;
+            uint4 w, gw;
             __nv_bfloat162* h = (__nv_bfloat162*)&w;
+            const __nv_bfloat162* gh = (const __nv_bfloat162*)&gw;
+            if (OPT && gel) {                          // eight gate values: 16 bytes at once where the row allows it
+              if (opt.gate_stride > 0 && (((uintptr_t)(gel + c0 + c)) & 15) == 0) gw = *(const uint4*)(gel + c0 + c);
+              else { bf16* gs = (bf16*)&gw;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) gs[e] = gel[c0 + c + e]; }
+            }
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               float a = __uint_as_float(v[c + 2 * q]) * inv, b = __uint_as_float(v[c + 2 * q + 1]) * inv;
               if (OPT && gel) {
-                a *= 1.0f / (1.0f + expf(-to_f32(gel[c0 + c + 2 * q])));
-                b *= 1.0f / (1.0f + expf(-to_f32(gel[c0 + c + 2 * q + 1])));
+                const float2 gq = __bfloat1622float2(gh[q]);
+                a *= sigm(gq.x);
+                b *= sigm(gq.y);
               }
               h[q] = __floats2bfloat162_rn(a, b);
             }
