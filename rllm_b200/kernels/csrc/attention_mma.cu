@@ -35,13 +35,18 @@
 //   gate        a row of gate pre-activations per token: the result is multiplied by sigmoid(gate[h])
 //               (gate_mode 1, one number a head) or sigmoid(gate[h * d + i]) (gate_mode 2, one an element).
 // The plain forms are compiled without any of it.
+//   bias, mag   (decode form, with the rotation and the cache write fused in) float32 [nq d + nkv d + nkv d]
+//               added to the token's q, k and v ahead of the rotation; cosine and sine times mag.
 struct AttnOpts {
   int keep_first, chunk;
   float softcap;
   const float* sinks;
   const bf16* gate;
   int gate_stride, gate_mode;
+  const float* bias;
+  float mag;
 };
+#define ATTN_NO_OPTS AttnOpts{0, 0, 0.f, nullptr, nullptr, 0, 0, nullptr, 1.f}
 
 #define BM 64          // rows per CTA (prefill)
 #define BN 64          // keys per tile
@@ -627,7 +632,10 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
 #pragma unroll
   for (int i = 0; i < STAGES; ++i) issue(t_lo + i);
   // the rotation's angles depend on the position alone
-  for (int i = lane; i < half; i += 32) rope_cos_sin(pos, inv_freq[i], &sCS[i], &sCS[half + i]);
+  for (int i = lane; i < half; i += 32) {
+    rope_cos_sin(pos, inv_freq[i], &sCS[i], &sCS[half + i]);
+    if (OPT) { sCS[i] *= opt.mag; sCS[half + i] *= opt.mag; }
+  }
   if (!q_first) {
     pdl_wait();
     load_q();
@@ -642,14 +650,26 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
     *(uint4*)tile_ptr<D>(sQ, r, c) = qreg[i];
   }
   __syncwarp();
+  // (OPT: the biases join in float32 ahead of the rotation, and one rounding follows, as where prompt portions
+  // are prepared)
+  const float* bias_q = (OPT && opt.bias) ? opt.bias + (size_t)kvh * g * D : nullptr;
   for (int idx = lane; idx < g * half; idx += 32) {
     const int r = idx / half, i = idx - r * half;
     bf16* pa = tile_ptr<D>(sQ, r, i >> 3) + (i & 7);
     bf16* pb = tile_ptr<D>(sQ, r, (i + half) >> 3) + ((i + half) & 7);
-    const float a = to_f32(*pa), b = to_f32(*pb);
+    float a = to_f32(*pa), b = to_f32(*pb);
+    if (bias_q) { a += bias_q[r * D + i]; b += bias_q[r * D + i + half]; }
     const float cs = sCS[i], sn = sCS[half + i];
     *pa = from_f32<bf16>(a * cs - b * sn);
     *pb = from_f32<bf16>(b * cs + a * sn);
+  }
+  if (bias_q) {
+    const int rest = D - rotary_dim;
+    for (int idx = lane; idx < g * rest; idx += 32) {
+      const int r = idx / rest, i = rotary_dim + idx - r * rest;
+      bf16* px = tile_ptr<D>(sQ, r, i >> 3) + (i & 7);
+      *px = from_f32<bf16>(to_f32(*px) + bias_q[r * D + i]);
+    }
   }
   __syncwarp();
 
@@ -688,11 +708,13 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
         const bf16* kx = qrow_now + (size_t)(nq + kvh) * D;
         const bf16* vx = qrow_now + (size_t)(nq + nkv + kvh) * D;
         const int r = pos - j0;
+        const float* bias_k = (OPT && opt.bias) ? opt.bias + (size_t)(nq + kvh) * D : nullptr;
+        const float* bias_v = (OPT && opt.bias) ? opt.bias + (size_t)(nq + nkv + kvh) * D : nullptr;
         for (int i = lane; i < D; i += 32) {
-          float kv = to_f32(kx[i]);
-          if (i < half) kv = kv * sCS[i] - to_f32(kx[i + half]) * sCS[half + i];
-          else if (i < rotary_dim) kv = kv * sCS[i - half] + to_f32(kx[i - half]) * sCS[i];
-          const bf16 kb = from_f32<bf16>(kv), vb = vx[i];
+          float kv = to_f32(kx[i]) + (bias_k ? bias_k[i] : 0.f);
+          if (i < half) kv = kv * sCS[i] - (to_f32(kx[i + half]) + (bias_k ? bias_k[i + half] : 0.f)) * sCS[half + i];
+          else if (i < rotary_dim) kv = kv * sCS[i - half] + (to_f32(kx[i - half]) + (bias_k ? bias_k[i - half] : 0.f)) * sCS[i];
+          const bf16 kb = from_f32<bf16>(kv), vb = bias_v ? from_f32<bf16>(to_f32(vx[i]) + bias_v[i]) : vx[i];
           tile_ptr<D>(sK, r, i >> 3)[i & 7] = kb;
           tile_ptr<D>(sV, r, i >> 3)[i & 7] = vb;
           if (okp) { kcache[off + i] = kb; vcache[off + i] = vb; }
@@ -905,7 +927,7 @@ RLLM_EXPORT int rllm_attention_prefill_bf16(const void* q, int q_stride, void* o
                                             cudaStream_t stream) {
   return prefill_bf16<false>(q, q_stride, out, kcache, vcache, block_table, max_blocks, q_start, seq_lens, seq_begin,
                              seq_end, num_tokens, nq, nkv, d, page_size, num_pages, window, scale, err, stream,
-                             AttnOpts{0, 0, 0.f, nullptr, nullptr, 0, 0});
+                             ATTN_NO_OPTS);
 }
 
 static int check_opts(int window, int keep_first, int chunk, float softcap, const void* gate, int gate_stride,
@@ -927,7 +949,7 @@ RLLM_EXPORT int rllm_attention_prefill_bf16_opts(const void* q, int q_stride, vo
   if (check_opts(window, keep_first, chunk, softcap, gate, gate_stride, gate_mode)) return RLLM_E_BADARG;
   return prefill_bf16<true>(q, q_stride, out, kcache, vcache, block_table, max_blocks, q_start, seq_lens, seq_begin,
                             seq_end, num_tokens, nq, nkv, d, page_size, num_pages, window, scale, err, stream,
-                            AttnOpts{keep_first, chunk, softcap, sinks, (const bf16*)gate, gate_stride, gate_mode});
+                            AttnOpts{keep_first, chunk, softcap, sinks, (const bf16*)gate, gate_stride, gate_mode, nullptr, 1.f});
 }
 
 // floats of workspace that a decode call with these sizes needs
@@ -1054,23 +1076,26 @@ RLLM_EXPORT int rllm_attention_decode_bf16(void* qkv, int q_stride, void* out, v
                                            int* err, cudaStream_t stream) {
   return decode_bf16<false>(qkv, q_stride, out, kcache, vcache, block_table, max_blocks, seq_lens, num_seqs, max_seq_len,
                             nq, nkv, d, page_size, num_pages, window, scale, inv_freq, rotary_dim, write_kv, workspace,
-                            counters, err, stream, true, AttnOpts{0, 0, 0.f, nullptr, nullptr, 0, 0});
+                            counters, err, stream, true, ATTN_NO_OPTS);
 }
 
-// The same with the options of the head comment, for tokens whose keys and values are in the cache already
-// (no rotation and no cache write here); gate [num_seqs, gate_stride], a row per sequence.
+// The same with the options of the head comment; gate [num_seqs, gate_stride], a row per sequence.  With the
+// rotation and the cache write fused in (rotary_dim, write_kv as above), bias (float32 over a row's q, k and v
+// heads, or null) is added first and cosine and sine are multiplied by mag.
 RLLM_EXPORT int rllm_attention_decode_bf16_opts(void* q, int q_stride, void* out, void* kcache, void* vcache,
                                                 const int* block_table, int max_blocks, const int* seq_lens,
                                                 int num_seqs, int max_seq_len, int nq, int nkv, int d, int page_size,
                                                 int num_pages, int window, float scale, int keep_first, int chunk,
                                                 float softcap, const float* sinks, const void* gate, int gate_stride,
-                                                int gate_mode, float* workspace, int* counters, int* err,
-                                                cudaStream_t stream) {
+                                                int gate_mode, const double* inv_freq, int rotary_dim, int write_kv,
+                                                const float* bias, float mag, float* workspace, int* counters,
+                                                int* err, cudaStream_t stream) {
   if (check_opts(window, keep_first, chunk, softcap, gate, gate_stride, gate_mode)) return RLLM_E_BADARG;
+  if (bias && !write_kv) return RLLM_E_BADARG;       // (the biases belong to the step that writes the token's key)
   return decode_bf16<true>(q, q_stride, out, kcache, vcache, block_table, max_blocks, seq_lens, num_seqs, max_seq_len,
-                           nq, nkv, d, page_size, num_pages, window, scale, nullptr, 0, 0, workspace, counters, err,
-                           stream, false,
-                           AttnOpts{keep_first, chunk, softcap, sinks, (const bf16*)gate, gate_stride, gate_mode});
+                           nq, nkv, d, page_size, num_pages, window, scale, inv_freq, rotary_dim, write_kv, workspace,
+                           counters, err, stream, false,
+                           AttnOpts{keep_first, chunk, softcap, sinks, (const bf16*)gate, gate_stride, gate_mode, bias, mag});
 }
 
 // ---------------------------------------------------------------------------
@@ -1130,5 +1155,5 @@ RLLM_EXPORT int rllm_attention_decode_bf16_static(void* qkv, int q_stride, void*
   return decode_bf16<false>(qkv, q_stride, out, kcache, vcache, block_table, max_blocks, seq_lens, num_seqs,
                             max_seq_len, nq, nkv, d, page_size, num_pages, window, scale, inv_freq,
                             rotary_dim, write_kv, scratch, counters, err, stream, allow_small,
-                            AttnOpts{0, 0, 0.f, nullptr, nullptr, 0, 0});
+                            ATTN_NO_OPTS);
 }

@@ -570,7 +570,8 @@ def attention_decode_bf16(qkv: torch.Tensor, q_stride: int, out: torch.Tensor, k
                           inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0,
                           write_kv: bool = False, keep_first: int = 0, chunk: int = 0, softcap: float = 0.0,
                           sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                          gate_per_head: bool = False) -> None:
+                          gate_per_head: bool = False, bias: Optional[torch.Tensor] = None,
+                          magnitude: float = 1.0) -> None:
     """Split-KV tensor-core attention of sequences 0 .. num_seqs-1, one query token
     each: row s of ``qkv`` holds the token's q heads (and behind them its k and v
     heads if ``write_kv``), row s of ``out`` gets the result.  ``rotary_dim`` > 0
@@ -578,8 +579,9 @@ def attention_decode_bf16(qkv: torch.Tensor, q_stride: int, out: torch.Tensor, k
     v into the cache in the kernel.  ``max_seq_len`` bounds every length.  The
     workspace (float32, ``attention_decode_workspace`` elements) holds the splits'
     partial results; it is allocated here if not given.  ``keep_first``, ``chunk``, ``softcap``, ``sinks`` and
-    ``gate`` as in ``attention_simt_kv`` (gate: a row per sequence), for tokens that are rotated and in the
-    cache already (neither ``rotary_dim`` nor ``write_kv``)."""
+    ``gate`` as in ``attention_simt_kv`` (gate: a row per sequence).  With any of them, and the rotation and
+    cache write in the kernel, ``bias`` (float32 over a row's q, k and v heads) is added first and cosine and sine
+    are multiplied by ``magnitude``, as ``head_norm_kv_write`` does for prompt portions."""
     lib = build.load_library("attention_mma")
     _contig(out, "out"); _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
     assert qkv.dtype is torch.bfloat16 and kcache.dtype is torch.bfloat16 and out.dtype is torch.bfloat16
@@ -590,15 +592,18 @@ def attention_decode_bf16(qkv: torch.Tensor, q_stride: int, out: torch.Tensor, k
     if rotary_dim:
         assert inv_freq is not None and inv_freq.dtype is torch.float64 and inv_freq.numel() == rotary_dim // 2
     counters = _counters_for(qkv.device, num_seqs * nkv)
-    if keep_first or chunk or softcap or sinks is not None or gate is not None:
-        assert not rotary_dim and not write_kv
+    if keep_first or chunk or softcap or sinks is not None or gate is not None or bias is not None or magnitude != 1.0:
         gate_mode = _attention_opts_asserts(sinks, gate, gate_per_head, nq, d)
+        if bias is not None:
+            assert write_kv and bias.dtype is torch.float32 and bias.is_contiguous() and bias.numel() == (nq + 2 * nkv) * d
         _check(lib.rllm_attention_decode_bf16_opts(
             _ptr(qkv), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_table),
             c_int(block_table.shape[1]), _ptr(seq_lens), c_int(num_seqs), c_int(max_seq_len), c_int(nq), c_int(nkv),
             c_int(d), c_int(kcache.shape[2]), c_int(kcache.shape[0]), c_int(window), c_float(scale), c_int(keep_first),
             c_int(chunk), c_float(softcap), _ptr(sinks), _ptr(gate), c_int(gate.stride(0) if gate is not None else 0),
-            c_int(gate_mode), _ptr(workspace), _ptr(counters), _ptr(err), _stream()), "attention_decode_bf16_opts")
+            c_int(gate_mode), _ptr(inv_freq if rotary_dim else None), c_int(rotary_dim), c_int(1 if write_kv else 0),
+            _ptr(bias), c_float(magnitude), _ptr(workspace), _ptr(counters), _ptr(err), _stream()),
+            "attention_decode_bf16_opts")
         return
     _check(lib.rllm_attention_decode_bf16(_ptr(qkv), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache),
                                           _ptr(block_table), c_int(block_table.shape[1]), _ptr(seq_lens),

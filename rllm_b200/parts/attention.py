@@ -208,10 +208,18 @@ class PagedAttention(Mixer):
         writes = cache.writes and not self.shares_kv
         q_pad = torch.empty((T, self.nq * self.dp), dtype=qkv.dtype, device=qkv.device) if self.dp else None
         inv_freq, rd = self.position.fused_rotary(qkv.device)
-        ops.head_norm_kv_write(qkv, ctx.positions, ctx.token_seq, self.w_qn, self.w_kn, self.qk_eps or 0.0, table,
-                               cache.k, cache.v, self.nq, 0 if self.shares_kv else self.nkv, self.d, self.dv,
-                               ctx.err, write_kv=writes, q_out=q_pad, bias=self.b_qkv, inv_freq=inv_freq,
-                               rotary_dim=rd, magnitude=float(getattr(self.position, "magnitude", 1.0)))
+        mag = float(getattr(self.position, "magnitude", 1.0))
+        # single decoded tokens of a mixer with options, where the tensor-core decode kernel serves: bias,
+        # rotation and cache write ride in that kernel (the same arithmetic), and only the prompt portions'
+        # rows are prepared here
+        nd_fused = ctx.num_decode if (self.masked and self.qk_eps is None and writes and not self.dp and
+                                      self.dv == self.d and self.d % 16 == 0 and
+                                      ops.use_mma_attention(qkv.dtype, self.nq, self.nkv, self.d)) else 0
+        if T > nd_fused:
+            ops.head_norm_kv_write(qkv[nd_fused:], ctx.positions[nd_fused:], ctx.token_seq[nd_fused:], self.w_qn,
+                                   self.w_kn, self.qk_eps or 0.0, table, cache.k, cache.v, self.nq,
+                                   0 if self.shares_kv else self.nkv, self.d, self.dv, ctx.err, write_kv=writes,
+                                   q_out=q_pad, bias=self.b_qkv, inv_freq=inv_freq, rotary_dim=rd, magnitude=mag)
         d, dv = (self.dp, self.dp) if self.dp else (self.d, self.dv)
         if q_pad is not None:
             qkv = q_pad
@@ -226,9 +234,11 @@ class PagedAttention(Mixer):
         if dv == d and d % 16 == 0 and ops.use_mma_attention(qkv.dtype, self.nq, self.nkv, d):
             nd = ctx.num_decode
             if nd:
+                fused = dict(inv_freq=inv_freq, rotary_dim=rd, write_kv=True, bias=self.b_qkv, magnitude=mag) \
+                    if nd_fused else dict(write_kv=False)
                 ops.attention_decode_bf16(qkv, stride, out, cache.k, cache.v, table, ctx.seq_lens, nd,
                                           max(ctx.seq_lens_host[:nd]), self.nq, self.nkv, d, window, self.scale,
-                                          ctx.err, write_kv=False, **opts)
+                                          ctx.err, **fused, **opts)
             if T > nd:
                 if ops.use_tcgen05_attention(qkv.dtype, self.nq, self.nkv, d, cache.k.shape[2]):
                     ops.attention_prefill_tcgen05(qkv, stride, out, cache.k, cache.v, table, ctx.q_start,

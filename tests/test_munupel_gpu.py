@@ -497,3 +497,52 @@ def test_greedy_generation_through_the_entry_point(mu_dirs, dtype, name):
     assert any(g.graph is not None for g in llm.engine.runner.graphs.values())
     llm.engine.cache.check()
     assert llm.engine.cache.usage()["num_requests"] == 0
+
+
+@pytest.mark.parametrize("nq,nkv,d,rd,bias,kind", [(8, 2, 64, 32, True, "chunk"), (4, 4, 16, 16, True, "chunk"),
+                                                    (16, 1, 128, 64, False, "window"), (6, 2, 32, 0, True, "window")])
+def test_decode_with_bias_rotation_and_cache_write_in_the_attention_kernel(nq, nkv, d, rd, bias, kind):
+    """The decode attention that adds the biases, rotates (cosine and sine times the rule's factor) and writes
+    the token's key and value itself leaves the same bits in the cache as the kernel that prepares prompt
+    portions, and returns what the attention over those pages returns."""
+    from rllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(d + nq)
+    page, lens = 16, [1, 37, 300, 129]
+    S, mag = len(lens), 1.2079
+    per = [-(-n // page) for n in lens]
+    table = torch.full((S, max(per)), -1, dtype=torch.int32)
+    perm = torch.randperm(sum(per), generator=g)
+    at = 0
+    for s in range(S):
+        table[s, :per[s]] = perm[at:at + per[s]].to(torch.int32)
+        at += per[s]
+    kc = torch.randn(sum(per), nkv, page, d, generator=g).bfloat16().cuda()
+    vc = torch.randn(sum(per), nkv, page, d, generator=g).bfloat16().cuda()
+    gw = nq * d if kind == "chunk" else nq
+    width = (nq + 2 * nkv) * d + gw
+    width += (-width) % 8
+    rows = torch.randn(S, width, generator=g).bfloat16().cuda()
+    b = (torch.randn((nq + 2 * nkv) * d, generator=g) * 2).cuda() if bias else None
+    inv_freq = (10000.0 ** (-torch.arange(rd // 2, dtype=F64) * 2 / max(rd, 1))).cuda() if rd else None
+    sink = None if kind == "chunk" else torch.randn(nq, generator=g).cuda()
+    opts = dict(keep_first=0 if kind == "chunk" else 3, chunk=64 if kind == "chunk" else 0,
+                softcap=7.0 if kind == "chunk" else 0.0, sinks=sink, gate_per_head=kind != "chunk")
+    window = 0 if kind == "chunk" else 50
+    positions, tseq, err = i32([n - 1 for n in lens]), i32(list(range(S))), err_word()
+    # a: prepared by the glue kernel, then attention from the pages
+    qa, ka, va = rows.clone(), kc.clone(), vc.clone()
+    ops.head_norm_kv_write(qa, positions, tseq, None, None, 0.0, table.cuda(), ka, va, nq, nkv, d, d, err, bias=b,
+                           inv_freq=inv_freq, rotary_dim=rd, magnitude=mag)
+    oa = torch.empty(S, nq * d, dtype=torch.bfloat16, device="cuda")
+    ops.attention_decode_bf16(qa, width, oa, ka, va, table.cuda(), i32(lens), S, max(lens), nq, nkv, d, window, 0.2, err,
+                              gate=qa[:, (nq + 2 * nkv) * d: (nq + 2 * nkv) * d + gw], **opts)
+    # b: all of it in the attention kernel
+    qb, kb, vb = rows.clone(), kc.clone(), vc.clone()
+    ob = torch.empty_like(oa)
+    ops.attention_decode_bf16(qb, width, ob, kb, vb, table.cuda(), i32(lens), S, max(lens), nq, nkv, d, window, 0.2, err,
+                              inv_freq=inv_freq, rotary_dim=rd, write_kv=True, bias=b, magnitude=mag,
+                              gate=qb[:, (nq + 2 * nkv) * d: (nq + 2 * nkv) * d + gw], **opts)
+    assert int(err.item()) == 0
+    assert torch.equal(ka, kb) and torch.equal(va, vb)
+    assert not torch.equal(ka, kc) and not torch.equal(va, vc)
+    assert float((oa.float() - ob.float()).abs().max()) <= 2e-2 * float(oa.float().abs().max())
