@@ -454,12 +454,12 @@ FEVOLORN_SIZES = {
 def munupel(layers, width, heads, kv_heads, dim, window, keep, chunk, cap, ff, vocab):
     """layers of the pattern [window with kept first tokens and sinks, chunked with capped scores and biases]:
     parallel-residual layers of one layer norm, gated attention and a dense feed-forward."""
-    rot = {"base": 500000.0, "dims": dim // 2}
+    rot = {"base": 1000000.0, "dims": dim // 2}
     win = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
            "mask": {"size": window, "keep_first": keep}, "rot": rot}
     chk = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": cap,
            "mask": {"size": chunk},
-           "rot": dict(rot, scaling={"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0})}
+           "rot": dict(rot, scaling={"factor": 8.0, "original": 2048, "fast": 16.0, "slow": 2.0})}
     return {"architecture": "Munupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "max_positions": 8192,
             "layers": [{"type": "attention_2" if i % 2 == 0 else "attention", "mixer": win if i % 2 == 0 else chk,
                         "mlp": {"kind": "dense", "ff": ff}} for i in range(layers)]}
@@ -469,9 +469,9 @@ def munupel(layers, width, heads, kv_heads, dim, window, keep, chunk, cap, ff, v
 # feed-forward) of equal width, layers, heads, head size, feed-forward width and vocabulary.  The Llama sees
 # every earlier key; Munupel's layers see a window beside four kept tokens, or their chunk.
 MUNUPEL_SIZES = {
-    "w1024": dict(layers=4, width=1024, heads=16, kv_heads=4, dim=64, window=512, keep=4, chunk=1024, cap=30.0,
+    "w1024": dict(layers=4, width=1024, heads=16, kv_heads=4, dim=64, window=512, keep=4, chunk=1024, cap=50.0,
                   ff=2048, vocab=32768),
-    "w2048": dict(layers=4, width=2048, heads=16, kv_heads=4, dim=128, window=1024, keep=4, chunk=1024, cap=30.0,
+    "w2048": dict(layers=4, width=2048, heads=16, kv_heads=4, dim=128, window=1024, keep=4, chunk=1024, cap=50.0,
                   ff=4096, vocab=32768),
 }
 
