@@ -103,6 +103,85 @@ head_norm_kv_write_kernel(T* qkv, int stride, const int* positions, const int* t
   }
 }
 
+// The same without norm weights for bfloat16 rows whose heads are multiples of 8 wide and 16-byte aligned
+// (rd a multiple of 16, no wider cache rows): a thread takes 8 neighbouring elements of a head (16 bytes), or,
+// inside the rotated dims, the 8 elements at i .. i + 7 and their partners at i + rd / 2 ..; the arithmetic of
+// every element is that of the kernel above.  Items of a token: (nq + nkv) * dk / 8 of q and k, nkv * dv / 8 of v.
+__device__ __forceinline__ void hn_load8(const bf16* p, float* o) {
+  const uint4 a = *(const uint4*)p;
+  const __nv_bfloat162* h = (const __nv_bfloat162*)&a;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); o[2 * i] = f.x; o[2 * i + 1] = f.y; }
+}
+__device__ __forceinline__ void hn_store8(bf16* p, const float* v) {
+  uint4 a;
+  __nv_bfloat162* h = (__nv_bfloat162*)&a;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  *(uint4*)p = a;
+}
+
+__global__ void __launch_bounds__(256)
+head_kv_write_bf16x8_kernel(bf16* qkv, int stride, const int* positions, const int* token_seq, const int* block_table,
+                            int max_blocks, bf16* kcache, bf16* vcache, int T_tokens, int nq, int nkv, int dk, int dv,
+                            int page_size, int num_pages, int write_kv, const float* __restrict__ bias,
+                            const double* __restrict__ inv_freq, int rd, float mag, int* err) {
+  pdl_wait();
+  pdl_launch();
+  const int ck = dk >> 3, cv = dv >> 3;
+  const int per_tok = (nq + nkv) * ck + nkv * cv;
+  const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (item >= (long long)T_tokens * per_tok) return;
+  const int t = (int)(item / per_tok), it = (int)(item - (long long)t * per_tok);
+  const bool is_v = it >= (nq + nkv) * ck;
+  const int h = is_v ? (it - (nq + nkv) * ck) / cv : it / ck;          // head among the v heads, or among q then k
+  const int c = is_v ? (it - (nq + nkv) * ck) - h * cv : it - h * ck;  // which 8 elements of the head
+  const int half = rd >> 1;
+  if (!is_v && c * 8 >= half && c * 8 < rd) return;                    // partners: done by the thread of c - half / 8
+  const bool to_cache = is_v || h >= nq;
+  if (to_cache && !write_kv) return;
+  const int pos = positions[t];
+  bf16* row = qkv + (size_t)t * stride;
+  const size_t at = is_v ? (size_t)(nq + nkv) * dk + (size_t)h * dv + c * 8 : (size_t)h * dk + c * 8;
+  bf16* dst = row + at;
+  if (to_cache) {
+    const int s = token_seq[t];
+    const int blk = pos / page_size;
+    const int page = (blk < max_blocks) ? block_table[(size_t)s * max_blocks + blk] : -1;
+    if (page < 0 || page >= num_pages) { atomicOr(err, 2); return; }
+    const int kvh = is_v ? h : h - nq;
+    dst = is_v ? vcache + (((size_t)page * nkv + kvh) * page_size + pos % page_size) * dv + c * 8
+               : kcache + (((size_t)page * nkv + kvh) * page_size + pos % page_size) * dk + c * 8;
+  }
+  float a[8];
+  hn_load8(row + at, a);
+  if (bias) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) a[i] += bias[at + i];
+  }
+  if (is_v || c * 8 >= rd) {                                           // no rotation here
+    if (to_cache || bias) hn_store8(dst, a);
+    return;
+  }
+  float b[8];
+  hn_load8(row + at + half, b);
+  if (bias) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) b[i] += bias[at + half + i];
+  }
+  float lo[8], hi[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float cs, sn;
+    rope_cos_sin(pos, inv_freq[c * 8 + i], &cs, &sn);
+    cs *= mag; sn *= mag;
+    lo[i] = a[i] * cs - b[i] * sn;
+    hi[i] = b[i] * cs + a[i] * sn;
+  }
+  hn_store8(dst, lo);
+  hn_store8(dst + half, hi);
+}
+
 RLLM_EXPORT int rllm_head_norm_kv_write(void* qkv, int dtype, int stride, const int* positions, const int* token_seq,
                                         const void* wq, const void* wk, int w_dtype, float eps, const int* block_table,
                                         int max_blocks, void* kcache, void* vcache, int T, int nq, int nkv, int dk,
@@ -114,6 +193,16 @@ RLLM_EXPORT int rllm_head_norm_kv_write(void* qkv, int dtype, int stride, const 
   if (rd < 0 || rd > dk || (rd & 1) || (rd > 0 && !inv_freq)) return RLLM_E_BADARG;
   if (dkp > dk && !q_out) return RLLM_E_BADARG;          // padded keys want padded queries
   if (write_kv && (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !kcache || !vcache)) return RLLM_E_BADARG;
+  const int nkv_w = write_kv ? nkv : 0;
+  if (dtype == RLLM_DT_BF16 && !wq && !wk && !q_out && dkp == dk && dvp == dv && dk % 8 == 0 && dv % 8 == 0 &&
+      rd % 16 == 0 && stride % 8 == 0 && (((uintptr_t)qkv | (uintptr_t)kcache | (uintptr_t)vcache) & 15) == 0) {
+    const long long items = (long long)T * ((nq + nkv_w) * (dk / 8) + nkv_w * (dv / 8));
+    const unsigned blocks8 = (unsigned)((items + 255) / 256);
+    cudaError_t e8 = rllm_launch_pdl(head_kv_write_bf16x8_kernel, dim3(blocks8), dim3(256), (size_t)0, stream, (bf16*)qkv,
+                                     stride, positions, token_seq, block_table, max_blocks, (bf16*)kcache, (bf16*)vcache,
+                                     T, nq, nkv_w, dk, dv, page_size, num_pages, write_kv, bias, inv_freq, rd, mag, err);
+    return (int)e8;
+  }
   const long long warps = (long long)T * (nq + 2 * nkv);
   const unsigned blocks = (unsigned)((warps + HN_WARPS - 1) / HN_WARPS);
   RLLM_DISPATCH_DTYPE(dtype, TT, RLLM_DISPATCH_DTYPE(w_dtype, TW,

@@ -22,7 +22,10 @@ keys (normalised) and values are written to the pages by one kernel and the
 attention reads everything from there.
 
 More options, each with its constants as parameters; a mixer with any of them goes the same way (one
-kernel adds the biases, normalises, rotates and writes the pages; the attention reads from the pages):
+kernel adds the biases, normalises, rotates and writes the pages; the attention reads from the pages: the
+tcgen05 or the mma.sync kernel's form with options where keys and values have one size that it takes, else
+the CUDA-core kernel; for single decoded tokens the tensor-core decode kernel does the biases, the rotation
+and the cache write itself):
 ``bias`` True: q, k, v and the output projection have biases ("q_bias", "k_bias", "v_bias", "o_bias"),
 added in float32; ``softcap`` = c: a scaled score s becomes c tanh(s / c); ``chunk`` = n: a query at
 position p sees only keys j with floor(j / n) = floor(p / n), counted from the sequence's position 0;

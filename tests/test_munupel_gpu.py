@@ -70,6 +70,10 @@ def test_layer_norm_completes_the_stream_and_normalises_it(dtype, T, H):
                                              (4, 4, 16, 16, {"dims": 16, "base": 300.0, "scaling": {
                                                  "factor": 8.0, "original": 64, "fast": 16.0, "slow": 2.0}}),
                                              (2, 1, 64, 32, {"dims": 2, "base": 3.0}),
+                                             (8, 2, 64, 64, {"dims": 32, "base": 1000000.0, "scaling": {
+                                                 "factor": 8.0, "original": 2048, "fast": 16.0, "slow": 2.0}}),
+                                             (4, 1, 128, 64, {"dims": 128, "base": 10000.0}),
+                                             (2, 2, 32, 48, {"dims": 16, "base": 10000.0}),
                                              (3, 1, 20, 28, {"dims": 20, "base": 250000.0, "scaling": {
                                                  "factor": 3.0, "original": 256, "fast": 24.0, "slow": 1.5}})])
 def test_biases_and_rescaled_rotation_at_the_cache_write(dtype, nq, nkv, dk, dv, rot):
