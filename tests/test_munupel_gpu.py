@@ -550,3 +550,31 @@ def test_decode_with_bias_rotation_and_cache_write_in_the_attention_kernel(nq, n
     assert torch.equal(ka, kb) and torch.equal(va, vb)
     assert not torch.equal(ka, kc) and not torch.equal(va, vc)
     assert float((oa.float() - ob.float()).abs().max()) <= 2e-2 * float(oa.float().abs().max())
+
+
+def test_the_command_line_with_prefix_sharing_and_forked_samples(mu_dirs, capsys):
+    """`rllm generate` on a Munupel folder in float32: greedy tokens of the plain model for two prompts of which
+    the second repeats the first's 40 tokens (its pages are found again: the kept first pages and those the
+    first query sees) and goes on; then two sampled continuations of one prompt, which fork from its pages."""
+    import json
+    from rllm_b200.cli import main
+    V = MU_A["vocab"]
+    rng = np.random.default_rng(23)
+    first = [int(t) for t in rng.integers(0, V, size=40)]
+    second = first + [int(t) for t in rng.integers(0, V, size=9)]
+    ids = lambda p: ",".join(str(t) for t in p)
+    common = ["--dtype", "fp32", "--num-gpu-blocks", "64", "--block-size", "8", "--max-num-seqs", "2", "--ignore-eos",
+              "--json"]
+    code = main(["generate", mu_dirs["A"], "--prompt-ids", ids(first), "-p", ids(first), "-p", ids(second),
+                 "--max-tokens", "6", "--temperature", "0", "--enable-prefix-caching", "true"] + common)
+    assert code == 0
+    lines = [json.loads(l) for l in capsys.readouterr().out.strip().split("\n")]
+    cfg, w = pm.read_model_dir(mu_dirs["A"])
+    assert [l["token_ids"] for l in lines] == [plain_greedy(cfg, w, first, 6), plain_greedy(cfg, w, first, 6),
+                                               plain_greedy(cfg, w, second, 6)]
+    code = main(["generate", mu_dirs["A"], "--prompt-ids", ids(second), "--max-tokens", "5", "--temperature", "0.8",
+                 "-n", "2", "--seed", "3"] + common)
+    assert code == 0
+    line = json.loads(capsys.readouterr().out.strip())
+    assert [o["index"] for o in line["outputs"]] == [0, 1] and all(len(o["token_ids"]) == 5 for o in line["outputs"])
+    assert all(0 <= t < V for o in line["outputs"] for t in o["token_ids"])
