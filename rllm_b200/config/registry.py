@@ -52,4 +52,4 @@ def load_model_description(model_dir: str) -> Tuple[Any, Any]:
 
 def _ensure_builtin() -> None:
     # the built-in architecture registers itself on import
-    from ..models import fasulix, fevolorn, llama, munupel  # noqa: F401
+    from ..models import fasulix, fevolorn, llama, munupel, tibelix  # noqa: F401

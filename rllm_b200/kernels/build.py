@@ -38,7 +38,7 @@ NVCC_FLAGS = [
 
 SOURCES = ["elementwise", "attention_simt", "attention_mma", "attention_tcgen05", "gemm_f32", "gemm_small_m", "gemm_tcgen05", "sampling", "weights_rng",
            "layer_glue", "mingru", "latent_attention", "latent_attention_mma", "moe",
-           "hyper_streams", "mixer_glue", "lightning", "selective_scan", "layernorm"]
+           "hyper_streams", "mixer_glue", "lightning", "selective_scan", "layernorm", "mlstm"]
 
 _lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}

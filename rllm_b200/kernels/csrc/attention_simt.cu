@@ -19,7 +19,9 @@
 //   sinks       float32 [nq]: exp(sinks[h]) joins the softmax's denominator (no key, no value, unscaled);
 //   gate        a row of gate pre-activations beside the token's queries: the result is multiplied by
 //               sigmoid(gate[h]) (gate_mode 1, one number a head) or sigmoid(gate[h * dv + i])
-//               (gate_mode 2, one a result element).
+//               (gate_mode 2, one a result element);
+//   slopes      float32 [nq]: slopes[h] * (p - j) is taken off the score of key j (after scaling and cap):
+//               a bias that grows with the distance between query and key.
 //
 // Keys are walked in groups of 32 aligned to absolute positions, so the
 // arithmetic of a row does not depend on how the sequence was cut into steps,
@@ -56,7 +58,8 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
                       const int* __restrict__ positions, const int* __restrict__ token_seq, int T_tokens,
                       int nq, int nkv, int d, int dv, int page_size, int num_pages, int window, float scale,
                       int keep_first, int chunk, float softcap, const float* __restrict__ sinks,
-                      const T* __restrict__ gate, int gate_stride, int gate_mode, int* __restrict__ err) {
+                      const T* __restrict__ gate, int gate_stride, int gate_mode,
+                      const float* __restrict__ slopes, int* __restrict__ err) {
   extern __shared__ float qs[];  // [ATT_WARPS][d]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const long long gw = (long long)blockIdx.x * ATT_WARPS + warp;
@@ -72,6 +75,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
   const int kept_end = (window > 0 && keep_first > 0) ? min(min(keep_first, kstart), kend) : 0;
   const int kept_start = (chunk > 0) ? min(qpos / chunk * chunk, kept_end) : 0;
   const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
+  const float slope = slopes ? slopes[h] : 0.f;
   float* myq = qs + warp * d;
   const T* qrow = q + (size_t)t * q_stride + (size_t)h * d;
   for (int i = lane; i < d; i += 32) myq[i] = to_f32(qrow[i]);
@@ -110,6 +114,7 @@ attention_simt_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out
         }
         score = dot * scale;
         if (softcap > 0.f) score = softcap * tanhf(score * inv_cap);
+        if (slopes) score -= slope * (float)(qpos - j);
       }
     }
     const float cmax = warp_max(score);
@@ -164,8 +169,8 @@ RLLM_EXPORT int rllm_attention_simt_kv(const void* q, int q_stride, void* out, c
                                        int max_blocks, const int* positions, const int* token_seq, int T,
                                        int nq, int nkv, int d, int dv, int page_size, int num_pages, int window,
                                        float scale, int keep_first, int chunk, float softcap, const float* sinks,
-                                       const void* gate, int gate_stride, int gate_mode, int* err,
-                                       cudaStream_t stream) {
+                                       const void* gate, int gate_stride, int gate_mode, const float* slopes,
+                                       int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || dv <= 0 || page_size <= 0 || num_pages <= 0 ||
       max_blocks <= 0 || window < 0 || keep_first < 0 || chunk < 0 || !(softcap >= 0.f) || gate_mode < 0 ||
@@ -181,7 +186,7 @@ RLLM_EXPORT int rllm_attention_simt_kv(const void* q, int q_stride, void* out, c
     (attention_simt_kernel<T_, VEC_><<<blocks, 32 * ATT_WARPS, smem, stream>>>(                             \
         (const T_*)q, q_stride, (T_*)out, (const T_*)kcache, (const T_*)vcache, block_table,                \
         max_blocks, positions, token_seq, T, nq, nkv, d, dv, page_size, num_pages, window, scale, keep_first,  \
-        chunk, softcap, sinks, (const T_*)gate, gate_stride, gate_mode, err)))
+        chunk, softcap, sinks, (const T_*)gate, gate_stride, gate_mode, slopes, err)))
   if (vec) ATT_GO(true); else ATT_GO(false);
 #undef ATT_GO
   RLLM_LAUNCH_CHECK();
@@ -197,5 +202,5 @@ RLLM_EXPORT int rllm_attention_simt(const void* q, int q_stride, void* out, cons
   if (q_stride % 8 != 0) return RLLM_E_BADARG;
   return rllm_attention_simt_kv(q, q_stride, out, kcache, vcache, dtype, block_table, max_blocks, positions,
                                 token_seq, T, nq, nkv, d, d, page_size, num_pages, window, scale, 0, 0, 0.f, nullptr,
-                                nullptr, 0, 0, err, stream);
+                                nullptr, 0, 0, nullptr, err, stream);
 }

@@ -445,6 +445,51 @@ RLLM_EXPORT int rllm_act_mul(const void* gu, void* out, int dtype, int T, int I,
   return 0;
 }
 
+// out[t, i] = act(x[t, i]) without a second factor; act 0: silu, 1: tanh-gelu, 2: the square of relu.
+// sigmoid_gate: out[t, i] = x[t, i] * sigmoid(g[t, i]), g a column slice with its own row stride.
+template <typename T>
+__global__ void act_kernel(const T* x, T* out, size_t n, int act) {   // out may be x
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n) return;
+  const float g = to_f32(x[idx]);
+  float a;
+  if (act == 2) { const float r = fmaxf(g, 0.f); a = r * r; }
+  else if (act == 1) a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  else a = g / (1.0f + expf(-g));
+  out[idx] = from_f32<T>(a);
+}
+
+RLLM_EXPORT int rllm_act(const void* x, void* out, int dtype, long long n, int act, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (act < 0 || act > 2) return RLLM_E_BADARG;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  RLLM_DISPATCH_DTYPE(dtype, T_, (act_kernel<T_><<<blocks, 256, 0, stream>>>((const T_*)x, (T_*)out, (size_t)n, act)));
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
+template <typename T>
+__global__ void sigmoid_gate_kernel(const T* x, const T* g, int g_stride, T* out,   // out may be x
+                                    int W, size_t n) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n) return;
+  const size_t t = idx / W;
+  const int i = (int)(idx - t * W);
+  out[idx] = from_f32<T>(to_f32(x[idx]) / (1.0f + expf(-to_f32(g[t * g_stride + i]))));
+}
+
+RLLM_EXPORT int rllm_sigmoid_gate(const void* x, const void* g, int g_stride, void* out, int dtype, int T, int W,
+                                  cudaStream_t stream) {
+  if (T <= 0 || W <= 0) return 0;
+  if (g_stride < W) return RLLM_E_BADARG;
+  const size_t n = (size_t)T * W;
+  const unsigned blocks = (unsigned)((n + 255) / 256);
+  RLLM_DISPATCH_DTYPE(dtype, T_, (sigmoid_gate_kernel<T_><<<blocks, 256, 0, stream>>>((const T_*)x, (const T_*)g, g_stride,
+                                                                                      (T_*)out, W, n)));
+  RLLM_LAUNCH_CHECK();
+  return 0;
+}
+
 RLLM_EXPORT int rllm_silu_mul(const void* gu, void* out, int dtype, int T, int I, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (I <= 0) return RLLM_E_BADARG;

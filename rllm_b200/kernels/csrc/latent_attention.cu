@@ -40,7 +40,7 @@ latent_prep_kernel(const T* a, int a_stride, int q_rank, int kv_rank, int rot, i
                    const TW* wq, const TW* wkv, float eps, T* cq,
                    T* cache, const int* block_table, int max_blocks,
                    const int* positions, const int* token_seq,
-                   const double* inv_freq, int page_size, int num_pages, int write_kv,
+                   const double* inv_freq, float mag, int page_size, int num_pages, int write_kv,
                    int* err) {
   // (Every kernel of this file starts with the wait for the kernel ahead of it in the stream and lets the
   // next one in right after: launches overlap the tails of their predecessors.  The pointer parameters
@@ -78,6 +78,7 @@ latent_prep_kernel(const T* a, int a_stride, int q_rank, int kv_rank, int rot, i
     if (2 * i + 1 < rot_dims) {
       float c, sn;
       rot_cos_sin<T>(pos, inv_freq[i], &c, &sn);
+      c *= mag; sn *= mag;              // the factor that a rescaled rotation puts on cosine and sine (1: none)
       dst[kv_rank + 2 * i] = from_f32<T>(u * c - v * sn);
       dst[kv_rank + 2 * i + 1] = from_f32<T>(v * c + u * sn);
     } else {
@@ -90,8 +91,9 @@ latent_prep_kernel(const T* a, int a_stride, int q_rank, int kv_rank, int rot, i
 RLLM_EXPORT int rllm_latent_prep(const void* a, int a_stride, int q_rank, int kv_rank, int rot, int rot_dims,
                                  const void* wq, const void* wkv, float eps, void* cq, void* cache,
                                  const int* block_table, int max_blocks, const int* positions,
-                                 const int* token_seq, const double* inv_freq, int page_size, int num_pages,
-                                 int write_kv, int T, int dtype, int w_dtype, int* err, cudaStream_t stream) {
+                                 const int* token_seq, const double* inv_freq, float mag, int page_size,
+                                 int num_pages, int write_kv, int T, int dtype, int w_dtype, int* err,
+                                 cudaStream_t stream) {
   if (T <= 0) return 0;
   if (q_rank <= 0 || (write_kv && (kv_rank <= 0 || rot < 0 || (rot & 1) || rot_dims > rot || (rot_dims & 1) ||
                                    page_size <= 0 || num_pages <= 0 || max_blocks <= 0)))
@@ -99,7 +101,7 @@ RLLM_EXPORT int rllm_latent_prep(const void* a, int a_stride, int q_rank, int kv
 #define LP_LAUNCH(T_, TW_)                                                                                \
   rllm_launch_pdl(latent_prep_kernel<T_, TW_>, dim3(T), dim3(128), (size_t)(0), stream, (const T_*)a, a_stride, q_rank, kv_rank, rot, rot_dims, \
       (const TW_*)wq, (const TW_*)wkv, eps, (T_*)cq, (T_*)cache, block_table, max_blocks, positions,      \
-      token_seq, inv_freq, page_size, num_pages, write_kv, err)
+      token_seq, inv_freq, mag, page_size, num_pages, write_kv, err)
   RLLM_DISPATCH_DTYPE(dtype, TT, RLLM_DISPATCH_DTYPE(w_dtype, TW, LP_LAUNCH(TT, TW)));
 #undef LP_LAUNCH
   RLLM_LAUNCH_CHECK();
@@ -111,7 +113,7 @@ RLLM_EXPORT int rllm_latent_prep(const void* a, int a_stride, int q_rank, int kv
 // ---------------------------------------------------------------------------
 template <typename T>
 __global__ void latent_q_rot_kernel(const T* q, T* qt, const int* positions,
-                                    const double* inv_freq, int heads, int dim, int rot,
+                                    const double* inv_freq, float mag, int heads, int dim, int rot,
                                     int rot_dims, int kv_rank, long long total) {
   pdl_wait();
   pdl_launch();
@@ -128,6 +130,7 @@ __global__ void latent_q_rot_kernel(const T* q, T* qt, const int* positions,
   if (2 * i + 1 < rot_dims) {
     float c, sn;
     rot_cos_sin<T>(positions[t], inv_freq[i], &c, &sn);
+    c *= mag; sn *= mag;
     dst[2 * i] = from_f32<T>(u * c - v * sn);
     dst[2 * i + 1] = from_f32<T>(v * c + u * sn);
   } else {
@@ -136,7 +139,7 @@ __global__ void latent_q_rot_kernel(const T* q, T* qt, const int* positions,
   }
 }
 
-RLLM_EXPORT int rllm_latent_q_rot(const void* q, void* qt, const int* positions, const double* inv_freq, int T,
+RLLM_EXPORT int rllm_latent_q_rot(const void* q, void* qt, const int* positions, const double* inv_freq, float mag, int T,
                                   int heads, int dim, int rot, int rot_dims, int kv_rank, int dtype,
                                   cudaStream_t stream) {
   const long long total = (long long)T * heads * (rot / 2);
@@ -144,7 +147,7 @@ RLLM_EXPORT int rllm_latent_q_rot(const void* q, void* qt, const int* positions,
   if (rot & 1 || rot_dims > rot || (rot_dims & 1)) return RLLM_E_BADARG;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   RLLM_DISPATCH_DTYPE(dtype, TT, (rllm_launch_pdl(latent_q_rot_kernel<TT>, dim3(blocks), dim3(256), (size_t)(0), stream, 
-      (const TT*)q, (TT*)qt, positions, inv_freq, heads, dim, rot, rot_dims, kv_rank, total)));
+      (const TT*)q, (TT*)qt, positions, inv_freq, mag, heads, dim, rot, rot_dims, kv_rank, total)));
   RLLM_LAUNCH_CHECK();
   return 0;
 }

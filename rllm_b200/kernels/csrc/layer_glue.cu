@@ -3,7 +3,7 @@
 // weighted sum of the results of all layers so far.  All arithmetic is float32;
 // the stream and the layer results are float32 in memory.
 //
-//   gated_postnorm_add:  v = (sum_k c[t, k] y[t, k, :]) * sigmoid(g[t, :] + b)
+//   gated_postnorm_add:  v = (sum_k c[t, k] y[t, k, :]) * sigmoid(g[t, :] + b)      (g absent: no gate)
 //                        x_out[t, :] = x_in[t, :] + v / sqrt(mean(v^2) + eps) * w
 //                        and, if asked, next[t, :] = x_out / sqrt(mean(x_out^2) + eps2) * w2
 //                        (the norm that reads the stream next).  With a history of layer results
@@ -43,8 +43,10 @@ gated_postnorm_add_kernel(const float* x_in, float* x_out, const TA* y,
       for (int k = 0; k < slots; ++k)
         v = fmaf(slot_w[(size_t)t * slots + k], to_f32(y[((size_t)t * slots + k) * H + i]), v);
     }
-    const float a = to_f32(gr[i]) + to_f32(gb[i]);
-    v *= 1.0f / (1.0f + expf(-a));
+    if (g != nullptr) {                                  // no gate: the sublayer's result as it is
+      const float a = to_f32(gr[i]) + (gb ? to_f32(gb[i]) : 0.f);
+      v *= 1.0f / (1.0f + expf(-a));
+    }
     row[i] = v;
     ss += v * v;
   }
@@ -78,7 +80,7 @@ RLLM_EXPORT int rllm_gated_postnorm_add(const float* x_in, float* x_out, const v
                                         const void* coeff, float* stream_out, int T, int H, int act_dtype,
                                         int w_dtype, cudaStream_t stream) {
   if (T <= 0) return 0;
-  if (H <= 0 || slots < 1 || g_stride < H) return RLLM_E_BADARG;
+  if (H <= 0 || slots < 1 || (g != nullptr && g_stride < H)) return RLLM_E_BADARG;
   if (hist != nullptr && (levels < 1 || coeff == nullptr || stream_out == nullptr)) return RLLM_E_BADARG;
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 200 * 1024) return RLLM_E_UNSUPPORTED;

@@ -11,7 +11,11 @@
 //                        order: a bias on every element of the row (float32 [nq dk + nkv dk + nkv dv]), the
 //                        norm, and a rotation of queries and keys by position over the first rd dims of a
 //                        head (dimension i with i + rd / 2, angle position * inv_freq[i], cosine and sine
-//                        times `mag`; float32 rows take them in float64).
+//                        times `mag`; float32 rows take them in float64).  `unit_norm`: the norm without
+//                        weights (queries and keys are divided by their root mean square and nothing
+//                        else).  `qt_every` > 0: a query at position p is multiplied by
+//                        1 + qt_coef * ln(floor((p + 1) / qt_every) + 1), a temperature that grows with
+//                        the position; keys are not.
 //   rms_mean             out = (1/n) sum_i rms(x_i) * w_i  over n = 2 inputs of one width
 //                        (branches of a mixer that run side by side)
 //   gated_rmsnorm        out = rms(x) * w * sigmoid(g)     (x float32, g in the activation dtype)
@@ -30,7 +34,7 @@ head_norm_kv_write_kernel(T* qkv, int stride, const int* positions, const int* t
                           float eps, const int* block_table, int max_blocks, T* kcache, T* vcache, int T_tokens, int nq,
                           int nkv, int dk, int dv, int dkp, int dvp, T* q_out, int page_size, int num_pages,
                           int write_kv, const float* __restrict__ bias, const double* __restrict__ inv_freq, int rd,
-                          float mag, int* err) {
+                          float mag, int unit_norm, float qt_coef, int qt_every, int* err) {
   pdl_wait();
   pdl_launch();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -66,23 +70,26 @@ head_norm_kv_write_kernel(T* qkv, int stride, const int* positions, const int* t
   T* src = row + (size_t)h * dk;                          // query heads, then key heads: both dk wide
   const float* bs = bias ? bias + (size_t)h * dk : nullptr;
   const TW* w = (h < nq) ? wq : wk;
-  if (!w && !bs && rd == 0) {
+  const bool warm = h < nq && qt_every > 0;             // a query under a temperature that grows with its position
+  const bool scaled = w || unit_norm || warm;
+  if (!scaled && !bs && rd == 0) {
     if (dst) for (int i = lane; i < dkp; i += 32) dst[i] = (i < dk) ? src[i] : from_f32<T>(0.f);
     return;
   }
   float r = 1.0f;
-  if (w) {
+  if (w || unit_norm) {
     float ss = 0.f;
     for (int i = lane; i < dk; i += 32) { const float v = to_f32(src[i]) + (bs ? bs[i] : 0.f); ss = fmaf(v, v, ss); }
     ss = warp_sum(ss);
     r = 1.0f / sqrtf(ss / (float)dk + eps);
   }
+  if (warm) r *= 1.0f + qt_coef * logf((float)((pos + 1) / qt_every) + 1.0f);
   T* o = dst ? dst : src;
   const int half = rd >> 1;
   // a lane reads both members of its pairs before it writes them, and no other lane touches them: in place is safe
   for (int i = lane; i < half; i += 32) {
     float a = to_f32(src[i]) + (bs ? bs[i] : 0.f), b = to_f32(src[i + half]) + (bs ? bs[i + half] : 0.f);
-    if (w) { a *= r * to_f32(w[i]); b *= r * to_f32(w[i + half]); }
+    if (scaled) { a *= r * (w ? to_f32(w[i]) : 1.0f); b *= r * (w ? to_f32(w[i + half]) : 1.0f); }
     float c, sn;
     if (sizeof(T) == 4) {
       double sd, cd;
@@ -98,7 +105,7 @@ head_norm_kv_write_kernel(T* qkv, int stride, const int* positions, const int* t
   for (int i = rd + lane; i < (dst ? dkp : dk); i += 32) {
     if (i >= dk) { o[i] = from_f32<T>(0.f); continue; }
     float a = to_f32(src[i]) + (bs ? bs[i] : 0.f);
-    if (w) a *= r * to_f32(w[i]);
+    if (scaled) a *= r * (w ? to_f32(w[i]) : 1.0f);
     o[i] = from_f32<T>(a);
   }
 }
@@ -187,14 +194,15 @@ RLLM_EXPORT int rllm_head_norm_kv_write(void* qkv, int dtype, int stride, const 
                                         int max_blocks, void* kcache, void* vcache, int T, int nq, int nkv, int dk,
                                         int dv, int dkp, int dvp, void* q_out, int page_size, int num_pages,
                                         int write_kv, const float* bias, const double* inv_freq, int rd, float mag,
-                                        int* err, cudaStream_t stream) {
+                                        int unit_norm, float qt_coef, int qt_every, int* err, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (nq <= 0 || nkv < 0 || dk <= 0 || dv <= 0 || dkp < dk || dvp < dv) return RLLM_E_BADARG;
   if (rd < 0 || rd > dk || (rd & 1) || (rd > 0 && !inv_freq)) return RLLM_E_BADARG;
   if (dkp > dk && !q_out) return RLLM_E_BADARG;          // padded keys want padded queries
   if (write_kv && (page_size <= 0 || num_pages <= 0 || max_blocks <= 0 || !kcache || !vcache)) return RLLM_E_BADARG;
   const int nkv_w = write_kv ? nkv : 0;
-  if (dtype == RLLM_DT_BF16 && !wq && !wk && !q_out && dkp == dk && dvp == dv && dk % 8 == 0 && dv % 8 == 0 &&
+  if (qt_every < 0 || (unit_norm && (wq || wk))) return RLLM_E_BADARG;
+  if (dtype == RLLM_DT_BF16 && !wq && !wk && !unit_norm && qt_every == 0 && !q_out && dkp == dk && dvp == dv && dk % 8 == 0 && dv % 8 == 0 &&
       rd % 16 == 0 && stride % 8 == 0 && (((uintptr_t)qkv | (uintptr_t)kcache | (uintptr_t)vcache) & 15) == 0) {
     const long long items = (long long)T * ((nq + nkv_w) * (dk / 8) + nkv_w * (dv / 8));
     const unsigned blocks8 = (unsigned)((items + 255) / 256);
@@ -209,7 +217,7 @@ RLLM_EXPORT int rllm_head_norm_kv_write(void* qkv, int dtype, int stride, const 
     (rllm_launch_pdl(head_norm_kv_write_kernel<TT, TW>, dim3(blocks), dim3(32 * HN_WARPS), (size_t)0, stream, (TT*)qkv,
                      stride, positions, token_seq, (const TW*)wq, (const TW*)wk, eps, block_table, max_blocks,
                      (TT*)kcache, (TT*)vcache, T, nq, nkv, dk, dv, dkp, dvp, (TT*)q_out, page_size, num_pages,
-                     write_kv, bias, inv_freq, rd, mag, err))));
+                     write_kv, bias, inv_freq, rd, mag, unit_norm, qt_coef, qt_every, err))));
   RLLM_LAUNCH_CHECK();
   return 0;
 }

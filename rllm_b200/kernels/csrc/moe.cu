@@ -74,17 +74,20 @@ moe_route_kernel(const T* h, const T* wr, int* ids,
   }
 }
 
-// the same choice from logits that a matrix product left in float32: z [T, E]
+// the same choice from logits that a matrix product left in float32: z [T, E].
+// groups > 0: the experts form `groups` equal groups of neighbours; a group's score is the largest score in
+// it, and only experts of the `keep` groups with the largest scores (lowest index among equals) can be
+// chosen.  renorm: the chosen experts' weights are divided by their sum + 1e-20.
 __global__ void __launch_bounds__(32 * ROUTE_WARPS)
 moe_choose_kernel(const float* logits, int* ids, float* weights,
-                  int T_tokens, int E, int top) {
+                  int T_tokens, int E, int top, int groups, int keep, int renorm) {
   pdl_wait();
   pdl_launch();
-  extern __shared__ float zs[];   // [ROUTE_WARPS][E]
+  extern __shared__ float zs[];   // [ROUTE_WARPS][E + groups]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int t = blockIdx.x * ROUTE_WARPS + warp;
   if (t >= T_tokens) return;
-  float* z = zs + warp * E;
+  float* z = zs + warp * (E + groups);
   float mx = -INFINITY;
   for (int e = lane; e < E; e += 32) { z[e] = logits[(size_t)t * E + e]; mx = fmaxf(mx, z[e]); }
   mx = warp_max(mx);
@@ -93,6 +96,25 @@ moe_choose_kernel(const float* logits, int* ids, float* weights,
   sum = warp_sum(sum);
   for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - mx) / sum;
   __syncwarp();
+  if (groups > 0) {
+    float* gs = z + E;
+    const int per = E / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float b = -1.f;
+      for (int e = g * per; e < (g + 1) * per; ++e) { float v = z[e]; if (v != v) v = 0.f; b = fmaxf(b, v); }
+      gs[g] = b;
+    }
+    __syncwarp();
+    // a group stays if fewer than `keep` groups stand ahead of it (a larger score, or the same and a lower index)
+    for (int g = lane; g < groups; g += 32) {
+      int ahead = 0;
+      for (int o = 0; o < groups; ++o) ahead += (gs[o] > gs[g] || (gs[o] == gs[g] && o < g)) ? 1 : 0;
+      if (ahead >= keep)
+        for (int e = g * per; e < (g + 1) * per; ++e) z[e] = -2.f;
+    }
+    __syncwarp();
+  }
+  float total = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = -1.f;
     int bi = 0x7fffffff;
@@ -107,12 +129,17 @@ moe_choose_kernel(const float* logits, int* ids, float* weights,
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
     }
+    total += best;
     if (lane == 0) {
       ids[(size_t)t * top + k] = bi;
       weights[(size_t)t * top + k] = best;
       z[bi] = -2.f;
     }
     __syncwarp();
+  }
+  if (renorm && lane == 0) {
+    const float inv = 1.0f / (total + 1e-20f);
+    for (int k = 0; k < top; ++k) weights[(size_t)t * top + k] *= inv;
   }
 }
 
@@ -170,13 +197,15 @@ RLLM_EXPORT int rllm_moe_choose_sigmoid(const float* logits, const float* bias, 
   return 0;
 }
 
-RLLM_EXPORT int rllm_moe_choose(const float* logits, int* ids, float* weights, int T, int E, int top,
-                                cudaStream_t stream) {
+RLLM_EXPORT int rllm_moe_choose(const float* logits, int* ids, float* weights, int T, int E, int top, int groups,
+                                int keep, int renorm, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || E > 2048) return RLLM_E_BADARG;
+  if (groups < 0 || (groups > 0 && (E % groups || keep < 1 || keep > groups || keep * (E / groups) < top))) return RLLM_E_BADARG;
   const unsigned blocks = (unsigned)((T + ROUTE_WARPS - 1) / ROUTE_WARPS);
-  rllm_launch_pdl(moe_choose_kernel, dim3(blocks), dim3(32 * ROUTE_WARPS), (size_t)((size_t)ROUTE_WARPS * E * sizeof(float)), stream, 
-      logits, ids, weights, T, E, top);
+  rllm_launch_pdl(moe_choose_kernel, dim3(blocks), dim3(32 * ROUTE_WARPS),
+                  (size_t)((size_t)ROUTE_WARPS * (E + groups) * sizeof(float)), stream, logits, ids, weights, T, E, top, groups,
+                  keep, renorm);
   RLLM_LAUNCH_CHECK();
   return 0;
 }

@@ -624,6 +624,11 @@ def mma_attention_takes(nq: int, nkv: int, d: int) -> bool:
     return d in (16, 32, 64, 128) and nq % nkv == 0 and nq // nkv <= 16
 
 
+def mma_attention_takes_opts(opts: dict) -> bool:
+    """Whether the tensor-core attention kernels have every option of ``opts`` (the CUDA-core kernel has all)."""
+    return opts.get("slopes") is None
+
+
 def use_mma_attention(dtype: torch.dtype, nq: int, nkv: int, d: int) -> bool:
     """bfloat16 with a head size the tensor-core attention kernels take; other
     cases (float32, other head sizes) go to the CUDA-core kernel."""
@@ -677,13 +682,13 @@ def logprobs(logits: torch.Tensor, tokens: torch.Tensor, top_n: int):
 # ---------------------------------------------------------------------------
 # gated, normalised sublayer results and the depth-weighted stream (layer_glue.cu)
 # ---------------------------------------------------------------------------
-def gated_postnorm_add(x_in: torch.Tensor, x_out: torch.Tensor, y: torch.Tensor, gate: torch.Tensor,
-                       gate_bias: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+def gated_postnorm_add(x_in: torch.Tensor, x_out: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor],
+                       gate_bias: Optional[torch.Tensor], norm_weight: torch.Tensor, eps: float,
                        slot_weights: Optional[torch.Tensor] = None,
                        next_weight: Optional[torch.Tensor] = None, next_eps: float = 0.0,
                        depth=None) -> Optional[torch.Tensor]:
     """x_out = x_in + rmsnorm(v) * norm_weight with v = y * sigmoid(gate + gate_bias); x float32 [T, H]
-    (x_out may be x_in).  ``slot_weights`` float32 [T, K]: y is [T * K, H] and a token's K rows are added
+    (x_out may be x_in; ``gate`` None: v = y, no gate).  ``slot_weights`` float32 [T, K]: y is [T * K, H] and a token's K rows are added
     with these factors first.  ``gate`` [T, H] may be a column slice (row stride >= H).  With
     ``next_weight`` the RMS norm of the new x under that weight is returned in the activation dtype.
     ``depth`` = (history float32 [L, T, H] whose level ``levels - 1`` is ``x_out``, levels, coeff [levels],
@@ -707,15 +712,17 @@ def gated_postnorm_add(x_in: torch.Tensor, x_out: torch.Tensor, y: torch.Tensor,
         assert slot_weights.dtype is torch.float32 and slot_weights.shape[0] == T
         _contig(slot_weights, "slot_weights")
         slots = slot_weights.shape[1]
-    assert y.shape == (T * slots, H) and gate.shape == (T, H) and gate.dtype is y.dtype and gate.stride(1) == 1
-    assert gate_bias.dtype is norm_weight.dtype and gate_bias.numel() == H and norm_weight.numel() == H
+    assert y.shape == (T * slots, H) and norm_weight.numel() == H
+    if gate is not None:
+        assert gate.shape == (T, H) and gate.dtype is y.dtype and gate.stride(1) == 1
+        assert gate_bias.dtype is norm_weight.dtype and gate_bias.numel() == H
+    g_stride = 0 if gate is None else (gate.stride(0) if T > 1 else max(H, gate.stride(0)))
     nxt = None
     if next_weight is not None:
         assert next_weight.dtype is norm_weight.dtype and next_weight.numel() == H
         nxt = torch.empty((T, H), dtype=y.dtype, device=y.device)
     _check(lib.rllm_gated_postnorm_add(_ptr(x_in), _ptr(x_out), _ptr(y), c_int(slots), _ptr(slot_weights),
-                                       _ptr(gate), c_int(gate.stride(0) if T > 1 else max(H, gate.stride(0))),
-                                       _ptr(gate_bias), _ptr(norm_weight), c_float(eps), _ptr(next_weight),
+                                       _ptr(gate), c_int(g_stride), _ptr(gate_bias if gate is not None else None), _ptr(norm_weight), c_float(eps), _ptr(next_weight),
                                        _ptr(nxt), c_float(next_eps), _ptr(hist), c_longlong(level_stride),
                                        c_int(levels), _ptr(coeff), _ptr(stream_out), c_int(T), c_int(H),
                                        c_int(dtype_code(y.dtype)), c_int(dtype_code(norm_weight.dtype)),
@@ -792,11 +799,11 @@ def mingru_scan(zxg: torch.Tensor, bias_z: torch.Tensor, bias_x: torch.Tensor, s
 def latent_prep(a: torch.Tensor, q_rank: int, kv_rank: int, rot: int, rot_dims: int, wq: torch.Tensor,
                 wkv: Optional[torch.Tensor], eps: float, cq: torch.Tensor, cache: Optional[torch.Tensor],
                 block_table: Optional[torch.Tensor], positions: torch.Tensor, token_seq: torch.Tensor,
-                inv_freq: Optional[torch.Tensor], err: torch.Tensor) -> None:
+                inv_freq: Optional[torch.Tensor], err: torch.Tensor, magnitude: float = 1.0) -> None:
     """a [T, q_rank (+ kv_rank + rot)]: the down projections of a token side by side.  cq [T, q_rank] =
     rmsnorm(a[:, :q_rank]) * wq.  With a cache ([pages, 1, page_size, kv_rank + rot]) the token's row is
     written: rmsnorm of the next kv_rank values times wkv, then the last rot values, the first rot_dims
-    of them rotated by position (pairs 2i, 2i+1)."""
+    of them rotated by position (pairs 2i, 2i+1), cosine and sine times ``magnitude``."""
     lib = build.load_library("latent_attention")
     T = a.shape[0]
     write = cache is not None
@@ -814,19 +821,22 @@ def latent_prep(a: torch.Tensor, q_rank: int, kv_rank: int, rot: int, rot_dims: 
     _check(lib.rllm_latent_prep(_ptr(a), c_int(a.stride(0)), c_int(q_rank), c_int(kv_rank), c_int(rot),
                                 c_int(rot_dims), _ptr(wq), _ptr(wkv), c_float(eps), _ptr(cq), _ptr(cache),
                                 _ptr(block_table), c_int(max_blocks), _ptr(positions), _ptr(token_seq),
-                                _ptr(inv_freq), c_int(page_size), c_int(pages), c_int(1 if write else 0),
+                                _ptr(inv_freq), c_float(magnitude), c_int(page_size), c_int(pages),
+                                c_int(1 if write else 0),
                                 c_int(T), c_int(dtype_code(a.dtype)), c_int(dtype_code(wq.dtype)), _ptr(err),
                                 _stream()), "latent_prep")
 
 
 def latent_q_rot(q: torch.Tensor, qt: torch.Tensor, positions: torch.Tensor, inv_freq: Optional[torch.Tensor],
-                 heads: int, dim: int, rot: int, rot_dims: int, kv_rank: int) -> None:
-    """qt[t, h, kv_rank:] = q[t, h, dim:] with its first rot_dims values rotated by position."""
+                 heads: int, dim: int, rot: int, rot_dims: int, kv_rank: int, magnitude: float = 1.0) -> None:
+    """qt[t, h, kv_rank:] = q[t, h, dim:] with its first rot_dims values rotated by position (cosine and sine
+    times ``magnitude``)."""
     lib = build.load_library("latent_attention")
     T = q.shape[0]
     assert q.shape == (T, heads * (dim + rot)) and qt.shape == (T, heads * (kv_rank + rot)) and qt.dtype is q.dtype
     _contig(q, "q"); _contig(qt, "qt")
-    _check(lib.rllm_latent_q_rot(_ptr(q), _ptr(qt), _ptr(positions), _ptr(inv_freq), c_int(T), c_int(heads),
+    _check(lib.rllm_latent_q_rot(_ptr(q), _ptr(qt), _ptr(positions), _ptr(inv_freq), c_float(magnitude), c_int(T),
+                                 c_int(heads),
                                  c_int(dim), c_int(rot), c_int(rot_dims), c_int(kv_rank),
                                  c_int(dtype_code(q.dtype)), _stream()), "latent_q_rot")
 
@@ -933,16 +943,19 @@ def moe_route(h: torch.Tensor, w_router: torch.Tensor, top: int):
     return ids, scores
 
 
-def moe_choose(logits: torch.Tensor, top: int):
-    """``moe_route`` from router logits that a matrix product left in float32 [T, E]."""
+def moe_choose(logits: torch.Tensor, top: int, groups: int = 0, keep: int = 0, renormalise: bool = False):
+    """``moe_route`` from router logits that a matrix product left in float32 [T, E].  ``groups`` > 0: the
+    experts form that many equal groups of neighbours, a group's score is its largest expert score, and only
+    experts of the ``keep`` best groups can be chosen.  ``renormalise``: the chosen scores are divided by their
+    sum + 1e-20."""
     lib = build.load_library("moe")
     T, E = logits.shape
     assert logits.dtype is torch.float32
     _contig(logits, "logits")
     ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     scores = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    _check(lib.rllm_moe_choose(_ptr(logits), _ptr(ids), _ptr(scores), c_int(T), c_int(E), c_int(top), _stream()),
-           "moe_choose")
+    _check(lib.rllm_moe_choose(_ptr(logits), _ptr(ids), _ptr(scores), c_int(T), c_int(E), c_int(top), c_int(groups),
+                               c_int(keep), c_int(1 if renormalise else 0), _stream()), "moe_choose")
     return ids, scores
 
 
@@ -1016,6 +1029,28 @@ def moe_choose_sigmoid(logits: torch.Tensor, top: int, bias: Optional[torch.Tens
 
 
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+PLAIN_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu_squared": 2}
+
+
+def act(x: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out = act(x) element by element (float32 arithmetic); act "silu", "gelu_tanh" or "relu_squared"
+    (max(z, 0)^2); ``out`` may be ``x``."""
+    lib = build.load_library("elementwise")
+    assert x.shape == out.shape and x.dtype is out.dtype
+    _contig(x, "x"); _contig(out, "out")
+    _check(lib.rllm_act(_ptr(x), _ptr(out), c_int(dtype_code(out.dtype)), c_longlong(x.numel()),
+                        c_int(PLAIN_ACTIVATIONS[activation]), _stream()), "act")
+
+
+def sigmoid_gate(x: torch.Tensor, gate: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = x[t, i] * sigmoid(gate[t, i]); gate may be a column slice (row stride >= its width)."""
+    lib = build.load_library("elementwise")
+    T, W = x.shape
+    assert out.shape == x.shape and gate.shape == x.shape and gate.dtype is x.dtype and out.dtype is x.dtype
+    assert gate.stride(1) == 1
+    _contig(x, "x"); _contig(out, "out")
+    _check(lib.rllm_sigmoid_gate(_ptr(x), _ptr(gate), c_int(gate.stride(0) if T > 1 else max(W, gate.stride(0))),
+                                 _ptr(out), c_int(dtype_code(x.dtype)), c_int(T), c_int(W), _stream()), "sigmoid_gate")
 
 
 def act_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
@@ -1121,14 +1156,17 @@ def head_norm_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: to
                        block_table: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, nq: int, nkv: int,
                        dk: int, dv: int, err: torch.Tensor, write_kv: bool = True,
                        q_out: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
-                       inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0, magnitude: float = 1.0) -> None:
+                       inv_freq: Optional[torch.Tensor] = None, rotary_dim: int = 0, magnitude: float = 1.0,
+                       unit_norm: bool = False, q_temp=None) -> None:
     """qkv [T, nq dk + nkv dk + nkv dv]: every query head (in place) and key head is divided by its root mean
     square and multiplied by the weight [dk] (None: left as it is); keys and values go to the token's place in
     kcache [pages, nkv, page, dkp] and vcache [pages, nkv, page, dvp].  Cache rows wider than the heads (dkp > dk,
     dvp > dv) are filled up with zeros; the queries then go to ``q_out`` [T, nq * dkp], filled up alike.
     ``bias`` float32 [nq dk + nkv dk + nkv dv] is added to every row first; ``inv_freq`` float64 [rotary_dim / 2]
     with ``rotary_dim`` > 0 rotates the first rotary_dim dims of every query and key head by the token's position
-    (dimension i with i + rotary_dim / 2), cosine and sine times ``magnitude``.  Columns of qkv behind the
+    (dimension i with i + rotary_dim / 2), cosine and sine times ``magnitude``.  ``unit_norm``: the heads are
+    divided by their root mean square although there are no weights.  ``q_temp`` = (coef, every): a query at
+    position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1).  Columns of qkv behind the
     value heads are left alone."""
     lib = build.load_library("mixer_glue")
     T = qkv.shape[0]
@@ -1159,6 +1197,8 @@ def head_norm_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_seq: to
                                        c_int(dkp), c_int(dvp), _ptr(q_out),
                                        c_int(page_size), c_int(pages), c_int(1 if write_kv else 0), _ptr(bias),
                                        _ptr(inv_freq if rotary_dim else None), c_int(rotary_dim), c_float(magnitude),
+                                       c_int(1 if unit_norm else 0), c_float(q_temp[0] if q_temp else 0.0),
+                                       c_int(int(q_temp[1]) if q_temp else 0),
                                        _ptr(err), _stream()), "head_norm_kv_write")
 
 
@@ -1166,13 +1206,14 @@ def attention_simt_kv(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache:
                       block_table: torch.Tensor, positions: torch.Tensor, token_seq: torch.Tensor, nq: int, nkv: int,
                       window: int, scale: float, err: torch.Tensor, keep_first: int = 0, chunk: int = 0,
                       softcap: float = 0.0, sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                      gate_per_head: bool = False) -> None:
+                      gate_per_head: bool = False, slopes: Optional[torch.Tensor] = None) -> None:
     """``attention_simt`` where keys [pages, nkv, page, dk] and values [pages, nkv, page, dv] have sizes of their
     own: q rows of nq * dk, out [T, nq * dv]; any dk, dv up to 256.  ``keep_first``: with a window, the first
     that many keys of a sequence stay visible; ``chunk``: only keys of the query's own chunk of positions are;
     ``softcap``: scores become softcap * tanh(score / softcap); ``sinks`` float32 [nq]: exp(sink) joins each
     head's softmax denominator; ``gate`` [T, nq] (``gate_per_head``) or [T, nq * dv], a view with the rows'
-    stride: the result is multiplied by its sigmoid."""
+    stride: the result is multiplied by its sigmoid; ``slopes`` float32 [nq]: slopes[h] * (query position - key
+    position) is taken off every score."""
     lib = build.load_library("attention_simt")
     T, dk, dv = out.shape[0], kcache.shape[3], vcache.shape[3]
     _contig(out, "out"); _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
@@ -1187,7 +1228,7 @@ def attention_simt_kv(q: torch.Tensor, q_stride: int, out: torch.Tensor, kcache:
                                       c_int(dv), c_int(kcache.shape[2]), c_int(kcache.shape[0]), c_int(window),
                                       c_float(scale), c_int(keep_first), c_int(chunk), c_float(softcap), _ptr(sinks),
                                       _ptr(gate), c_int(gate.stride(0) if gate is not None else 0),
-                                      c_int(0 if gate is None else (1 if gate_per_head else 2)),
+                                      c_int(0 if gate is None else (1 if gate_per_head else 2)), _ptr(slopes),
                                       _ptr(err), _stream()), "attention_simt_kv")
 
 
@@ -1351,3 +1392,52 @@ def add_row_bias(y: torch.Tensor, bias: torch.Tensor) -> None:
     assert y.dim() == 2 and y.is_contiguous() and bias.dtype is torch.float32 and bias.numel() == y.shape[1]
     _check(lib.rllm_add_row_bias(_ptr(y), _ptr(bias), c_int(dtype_code(y.dtype)), c_int(y.shape[0]),
                                  c_int(y.shape[1]), _stream()), "add_row_bias")
+
+
+# ---------------------------------------------------------------------------
+# the matrix memory (mlstm.cu)
+# ---------------------------------------------------------------------------
+def mlstm_state_size(d: int, dv: int) -> int:
+    """float32 values a head keeps: S [d, dv], n [d] and the running maximum."""
+    return d * dv + d + 1
+
+
+def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gates: torch.Tensor, bias_i: torch.Tensor,
+               bias_f: torch.Tensor, cap: float, qscale: float, state: torch.Tensor, q_start: torch.Tensor,
+               slots: torch.Tensor, num_seqs: int, heads: int, d: int, dv: int, err: torch.Tensor) -> torch.Tensor:
+    """The mLSTM recurrence over this step's tokens of every sequence, in order, from and into the sequences'
+    state slots.  q, k [T, heads * d] and v [T, heads * dv]: column slices of one product's result (one row
+    stride); gates float32 [T, 2 heads]: pre-activations of the input gates, then of the forget gates;
+    ``cap``: both are capped as cap * tanh(z / cap) (0: not); q is multiplied by ``qscale``.
+    state float32 [slots, heads, d * dv + d + 1].  Returns o float32 [T, heads * dv]."""
+    lib = build.load_library("mlstm")
+    T = q.shape[0]
+    assert q.shape == (T, heads * d) and k.shape == (T, heads * d) and v.shape == (T, heads * dv)
+    assert q.dtype is k.dtype and k.dtype is v.dtype and q.stride(0) == k.stride(0) == v.stride(0)
+    assert q.stride(1) == 1 and k.stride(1) == 1 and v.stride(1) == 1
+    assert gates.dtype is torch.float32 and gates.shape == (T, 2 * heads) and gates.is_contiguous()
+    assert bias_i.dtype is torch.float32 and bias_f.dtype is torch.float32 and bias_i.numel() == heads == bias_f.numel()
+    assert state.dtype is torch.float32 and state.is_contiguous() and state.shape[1:] == (heads, mlstm_state_size(d, dv))
+    out = torch.empty((T, heads * dv), dtype=torch.float32, device=q.device)
+    _check(lib.rllm_mlstm_scan(_ptr(q), _ptr(k), _ptr(v), c_int(q.stride(0)), c_int(dtype_code(q.dtype)), _ptr(gates),
+                               _ptr(bias_i), _ptr(bias_f), c_float(cap), c_float(qscale), _ptr(state), _ptr(q_start),
+                               _ptr(slots), _ptr(out), c_int(num_seqs), c_int(heads), c_int(d), c_int(dv),
+                               c_int(state.shape[0]), _ptr(err), _stream()), "mlstm_scan")
+    return out
+
+
+def head_gated_rmsnorm(x: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, heads: int,
+                       out_dtype: torch.dtype) -> torch.Tensor:
+    """out = x / sqrt(mean over a head's values of x^2 + eps) * weight * sigmoid(gate); x float32 [T, heads * dv],
+    weight [heads * dv], gate [T, heads * dv] in ``out_dtype`` (may be a column slice)."""
+    lib = build.load_library("mlstm")
+    T, W = x.shape
+    assert x.dtype is torch.float32 and x.is_contiguous() and W % heads == 0 and weight.numel() == W
+    assert gate.shape == (T, W) and gate.dtype is out_dtype and gate.stride(1) == 1
+    _contig(weight, "weight")
+    out = torch.empty((T, W), dtype=out_dtype, device=x.device)
+    _check(lib.rllm_head_gated_rmsnorm(_ptr(x), _ptr(gate), c_int(gate.stride(0) if T > 1 else max(W, gate.stride(0))),
+                                       _ptr(weight), c_int(dtype_code(weight.dtype)), _ptr(out),
+                                       c_int(dtype_code(out_dtype)), c_int(T), c_int(heads), c_int(W // heads),
+                                       c_float(eps), _stream()), "head_gated_rmsnorm")
+    return out

@@ -1,6 +1,6 @@
 """Parts a layer is put together from.  Importing the package registers the
 built-in kinds."""
-from . import (attention, block, gated_block, hyper_block, latent_attention, lightning, mingru, mlp, norm,  # noqa: F401  (registration)
+from . import (attention, block, gated_block, hyper_block, latent_attention, lightning, mingru, mlp, mlstm, norm,  # noqa: F401  (registration)
                parallel, rotary, routed_experts, selective_scan)
 from .base import (FeedForward, KVCacheView, Mixer, Norm, Part, PositionEncoding, StateCacheView,
                    StepContext)

@@ -33,7 +33,13 @@ position p sees only keys j with floor(j / n) = floor(p / n), counted from the s
 positions; ``sinks`` True: exp(sink[h]) ("sink", one number a head) joins the softmax's denominator, with
 no key and no value; ``gate`` "head" or "element": the heads' outputs are multiplied by sigmoid(W_g x)
 ("g": [num_heads, hidden] or [num_heads * v_dim, hidden]) before the output projection; W_g is stacked
-under [Wq; Wk; Wv], so the gate comes out of the same product.
+under [Wq; Wk; Wv], so the gate comes out of the same product (a run that reads another's keys and
+values stacks it under its Wq); ``sinks`` "zero": the same term with a fixed score of 0 and no tensor (one is
+added to the denominator); ``qk_norm_weights`` False (with ``qk_norm``): the heads are divided by their root
+mean square and multiplied by nothing; ``q_temp`` = (coef, every): the query at position p is multiplied by
+1 + coef * ln(floor((p + 1) / every) + 1) after its norm; ``distance_slopes`` = x: slope_h * (p - j) is taken
+off the scaled score of key j, with slope_h = 2^(-x (h + 1) / num_heads) for head h (a bias linear in the
+distance, steeper for the first heads).
 
 params: hidden_size, num_heads, num_kv_heads, head_dim, window (None: all
 keys), scale (None: 1/sqrt(head_dim)), position (PartSpec), shares_kv (True:
@@ -81,6 +87,13 @@ class PagedAttention(Mixer):
         self.chunk = int(p["chunk"]) if p.get("chunk") else 0
         self.keep_first = int(p.get("keep_first") or 0)
         self.sinks = bool(p.get("sinks", False))
+        self.zero_sinks = p.get("sinks") == "zero"
+        self.qk_weights = bool(p.get("qk_norm_weights", True))
+        qt = p.get("q_temp")
+        self.q_temp = (float(qt[0]), int(qt[1])) if qt else None
+        if self.q_temp is not None and self.q_temp[1] < 1:
+            raise ValueError("q_temp = (coef, every) with every >= 1")
+        self.slope_exp = float(p["distance_slopes"]) if p.get("distance_slopes") is not None else None
         self.gate = p.get("gate")
         if self.gate not in (None, "head", "element"):
             raise ValueError(f"gate {self.gate!r}; known: None, 'head', 'element'")
@@ -89,7 +102,8 @@ class PagedAttention(Mixer):
         if self.softcap < 0 or self.chunk < 0 or self.keep_first < 0:
             raise ValueError("softcap, chunk and keep_first must not be negative")
         # what the kernels of the Llama's form do not have: these go through the pages
-        self.masked = bool(self.softcap or self.chunk or self.keep_first or self.sinks or self.gate)
+        self.masked = bool(self.softcap or self.chunk or self.keep_first or self.sinks or self.gate or
+                           self.q_temp or self.slope_exp is not None)
         # the Llama's form: rotation fused with the write
         self.plain = self.dv == self.d and self.qk_eps is None and not self.bias and not self.masked
         # keys and values of two sizes: where the larger one is a size of the tensor-core kernels, the pages keep
@@ -107,9 +121,9 @@ class PagedAttention(Mixer):
         if self.dv > 256:
             raise ValueError(f"v_dim {self.dv}: the attention kernels take value heads up to 256")
         names = dict(p.get("tensor_names") or ())
-        want = ["k", "o", "q", "v"] + (["k_norm", "q_norm"] if self.qk_eps is not None else []) + \
-            (["q_bias", "k_bias", "v_bias", "o_bias"] if self.bias else []) + (["sink"] if self.sinks else []) + \
-            (["g"] if self.gate else [])
+        want = ["k", "o", "q", "v"] + (["k_norm", "q_norm"] if self.qk_eps is not None and self.qk_weights else []) + \
+            (["q_bias", "k_bias", "v_bias", "o_bias"] if self.bias else []) + \
+            (["sink"] if self.sinks and not self.zero_sinks else []) + (["g"] if self.gate else [])
         if sorted(names) != sorted(want):
             raise ValueError(f"an attention spec names its weights: tensor_names with the keys {sorted(want)}")
         self.names = {k: str(v) for k, v in names.items()}
@@ -120,11 +134,13 @@ class PagedAttention(Mixer):
             raise ValueError("this mixer's kernels rotate halves; an interleaved rotation is not among them")
         if not self.plain and self.position.fused_rotary() is None:
             raise ValueError("attention through the pages takes a rotation that its kernel can apply, or none")
-        if self.shares_kv and (self.bias or self.gate):
-            raise ValueError("a run that reads another's keys and values takes no biases and no gate")
+        if self.shares_kv and self.bias:
+            raise ValueError("a run that reads another's keys and values takes no biases")
+        if not self.qk_weights and self.qk_eps is None:
+            raise ValueError("qk_norm_weights False goes with qk_norm")
         self.gate_width = 0 if not self.gate else (self.nq if self.gate == "head" else self.nq * self.dv)
         self.w_qn = self.w_kn = None
-        self.b_qkv = self.b_o = self.sink = None
+        self.b_qkv = self.b_o = self.sink = self.slopes = None
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
 
@@ -143,7 +159,7 @@ class PagedAttention(Mixer):
             specs += [TensorSpec(k, (self.nkv * self.d, self.hidden)),
                       TensorSpec(v, (self.nkv * self.dv, self.hidden))]
         specs.append(TensorSpec(o, (self.hidden, self.nq * self.dv)))
-        if self.qk_eps is not None:
+        if self.qk_eps is not None and self.qk_weights:
             specs.append(TensorSpec(self.prefix + self.names["q_norm"], (self.d,), role="vector",
                                     init=("one_plus_normal", 0.1)))
             if not self.shares_kv:
@@ -153,7 +169,7 @@ class PagedAttention(Mixer):
             for key, n in (("q_bias", self.nq * self.d), ("k_bias", self.nkv * self.d), ("v_bias", self.nkv * self.dv),
                            ("o_bias", self.hidden)):
                 specs.append(TensorSpec(self.prefix + self.names[key], (n,), role="vector", init=("normal", 0.1)))
-        if self.sinks:
+        if self.sinks and not self.zero_sinks:
             specs.append(TensorSpec(self.prefix + self.names["sink"], (self.nq,), role="vector", init=("normal", 1.0)))
         if self.gate:
             specs.append(TensorSpec(self.prefix + self.names["g"], (self.gate_width, self.hidden)))
@@ -162,7 +178,12 @@ class PagedAttention(Mixer):
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         q, k, v, o = self._names()
         if self.shares_kv:
-            self.w_qkv = tensors[q]
+            # with a gate [Wq; Wg]: the gate's pre-activations lie behind the query heads
+            stack = [tensors[q]] + ([tensors[self.prefix + self.names["g"]]] if self.gate else [])
+            rows = sum(t.shape[0] for t in stack)
+            if self.gate and rows % 8:
+                stack.append(stack[0].new_zeros((8 - rows % 8, self.hidden)))
+            self.w_qkv = torch.cat(stack, dim=0).contiguous() if self.gate else tensors[q]
         else:
             # stacked [Wq; Wk; Wv]: one matrix product gives a token's q, k and v side by side
             # (with a gate: [Wq; Wk; Wv; Wg], and the gate's pre-activations lie behind the value heads)
@@ -179,14 +200,19 @@ class PagedAttention(Mixer):
             self.b_qkv = torch.cat([tensors[self.prefix + self.names[key]].float()
                                     for key in ("q_bias", "k_bias", "v_bias")]).contiguous()
             self.b_o = tensors[self.prefix + self.names["o_bias"]].float().contiguous()
-        if self.sinks:
+        if self.zero_sinks:
+            self.sink = torch.zeros(self.nq, dtype=torch.float32, device=self.w_o.device)
+        elif self.sinks:
             self.sink = tensors[self.prefix + self.names["sink"]].float().contiguous()
+        if self.slope_exp is not None:
+            self.slopes = torch.tensor([2.0 ** (-self.slope_exp * (h + 1) / self.nq) for h in range(self.nq)],
+                                       dtype=torch.float32, device=self.w_o.device)
         if self.dp and self.dv < self.dp:
             # the attention's result has dp columns a head, the last ones zeros: the projection skips them
             w = self.w_o.new_zeros((self.hidden, self.nq, self.dp))
             w[:, :, :self.dv] = self.w_o.view(self.hidden, self.nq, self.dv)
             self.w_o = w.view(self.hidden, self.nq * self.dp).contiguous()
-        if self.qk_eps is not None:
+        if self.qk_eps is not None and self.qk_weights:
             self.w_qn = tensors[self.prefix + self.names["q_norm"]].contiguous()
             self.w_kn = self.w_qn if self.shares_kv else \
                 tensors[self.prefix + self.names["k_norm"]].to(self.w_qn.dtype).contiguous()
@@ -215,14 +241,16 @@ class PagedAttention(Mixer):
         # single decoded tokens of a mixer with options, where the tensor-core decode kernel serves: bias,
         # rotation and cache write ride in that kernel (the same arithmetic), and only the prompt portions'
         # rows are prepared here
-        nd_fused = ctx.num_decode if (self.masked and self.qk_eps is None and writes and not self.dp and
+        nd_fused = ctx.num_decode if (self.masked and self.qk_eps is None and not self.q_temp and writes and
+                                      not self.dp and self.slopes is None and
                                       self.dv == self.d and self.d % 16 == 0 and
                                       ops.use_mma_attention(qkv.dtype, self.nq, self.nkv, self.d)) else 0
         if T > nd_fused:
             ops.head_norm_kv_write(qkv[nd_fused:], ctx.positions[nd_fused:], ctx.token_seq[nd_fused:], self.w_qn,
                                    self.w_kn, self.qk_eps or 0.0, table, cache.k, cache.v, self.nq,
                                    0 if self.shares_kv else self.nkv, self.d, self.dv, ctx.err, write_kv=writes,
-                                   q_out=q_pad, bias=self.b_qkv, inv_freq=inv_freq, rotary_dim=rd, magnitude=mag)
+                                   q_out=q_pad, bias=self.b_qkv, inv_freq=inv_freq, rotary_dim=rd, magnitude=mag,
+                                   unit_norm=self.qk_eps is not None and not self.qk_weights, q_temp=self.q_temp)
         d, dv = (self.dp, self.dp) if self.dp else (self.d, self.dv)
         if q_pad is not None:
             qkv = q_pad
@@ -230,11 +258,14 @@ class PagedAttention(Mixer):
         window, stride = int(self.window or 0), qkv.shape[1]
         gate = None
         if self.gate:
-            at = self.nq * self.d + self.nkv * (self.d + self.dv)
+            at = self.nq * self.d + (0 if self.shares_kv else self.nkv * (self.d + self.dv))
             gate = qkv[:, at: at + self.gate_width]
         opts = dict(keep_first=self.keep_first, chunk=self.chunk, softcap=self.softcap, sinks=self.sink, gate=gate,
                     gate_per_head=self.gate == "head") if self.masked else {}
-        if dv == d and d % 16 == 0 and ops.use_mma_attention(qkv.dtype, self.nq, self.nkv, d):
+        if self.slopes is not None:
+            opts["slopes"] = self.slopes
+        if dv == d and d % 16 == 0 and ops.use_mma_attention(qkv.dtype, self.nq, self.nkv, d) and \
+                ops.mma_attention_takes_opts(opts):
             nd = ctx.num_decode
             if nd:
                 fused = dict(inv_freq=inv_freq, rotary_dim=rd, write_kv=True, bias=self.b_qkv, magnitude=mag) \

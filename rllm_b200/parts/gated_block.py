@@ -21,6 +21,10 @@ joins the mixer's own first product where the mixer stacks its input weights
 norms: four (norm_0 .. norm_3).  params: hidden_size, depth_levels (0: none),
 tensor_names (keys "gate1", "gate1_bias", "gate2", "gate2_bias", "depth": names
 below the layer's prefix).
+
+``sandwich``: the same arrangement without the gates (m = mixer(a), f = ffn(b)) and
+without tensors of its own: x <- x + norm_1(mixer(norm_0(x))), x <- x + norm_3(ffn(norm_2(x))).
+The kernels are the same ones, told that there is no gate.  params: hidden_size.
 """
 from __future__ import annotations
 
@@ -40,6 +44,7 @@ _KEYS = ("gate1", "gate1_bias", "gate2", "gate2_bias", "depth")
 @register_part("block", "sandwich_gated")
 class SandwichGatedBlock(Part):
     takes_next_norm = True
+    gated = True
 
     def __init__(self, mixer: Mixer, ffn: Optional[FeedForward], norms: List[Norm], spec: PartSpec, prefix: str = ""):
         super().__init__(spec, prefix)
@@ -53,7 +58,10 @@ class SandwichGatedBlock(Part):
         self.hidden = int(p["hidden_size"])
         self.depth_levels = int(p.get("depth_levels") or 0)
         names = dict(p.get("tensor_names") or ())
-        if sorted(names) != sorted(_KEYS):
+        if not self.gated:
+            if names or self.depth_levels:
+                raise ValueError("a sandwich block has no tensors of its own and no depth-weighted stream")
+        elif sorted(names) != sorted(_KEYS):
             raise ValueError(f"a sandwich_gated spec names its tensors: tensor_names with the keys {_KEYS}")
         self.names = {k: prefix + str(v) for k, v in names.items()}
         self.w_g1 = self.b_g1 = self.w_g2 = self.b_g2 = self.depth = None
@@ -68,6 +76,8 @@ class SandwichGatedBlock(Part):
             ([self.norms[2], self.ffn, self.norms[3]] if self.ffn is not None else [])
 
     def tensor_specs(self) -> List[TensorSpec]:
+        if not self.gated:
+            return []
         n, H = self.names, self.hidden
         specs = [TensorSpec(n["gate1"], (H, H)), TensorSpec(n["gate1_bias"], (H,), role="vector", init=("normal", 0.5))]
         if self.ffn is not None:
@@ -82,9 +92,12 @@ class SandwichGatedBlock(Part):
         carries them all the same is no error."""
         if self.ffn is not None:
             return []
-        return [self.names["gate2"], self.names["gate2_bias"]] + [n.name for n in self.norms[2:] if hasattr(n, "name")]
+        return ([self.names["gate2"], self.names["gate2_bias"]] if self.gated else []) + \
+            [n.name for n in self.norms[2:] if hasattr(n, "name")]
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        if not self.gated:
+            return
         n = self.names
         self.w_g1, self.b_g1 = tensors[n["gate1"]], tensors[n["gate1_bias"]].contiguous()
         self._stacked = None
@@ -110,6 +123,8 @@ class SandwichGatedBlock(Part):
             x = h
         nxt_w = getattr(next_norm, "weight", None) if next_norm is not None and hasattr(next_norm, "eps") else None
         nxt_eps = float(next_norm.eps) if nxt_w is not None else 0.0
+        if not self.gated:
+            self._stacked = False
         if self._stacked is None:
             # the mixer's gate reads the mixer's input: one product with the mixer's own first one, if it can
             self._stacked = bool(self.mixer.stack_input(self.w_g1))
@@ -119,7 +134,7 @@ class SandwichGatedBlock(Part):
             m, g = self.mixer.forward(a, ctx, cache, side=True)
         else:
             m = self.mixer.forward(a, ctx, cache)
-            g = linear(a, self.w_g1)
+            g = linear(a, self.w_g1) if self.gated else None
         last = self.ffn is None
         # the sublayer that ends the layer also takes the depth average and the next layer's first norm
         stream = torch.empty_like(h) if self.depth_levels else None
@@ -133,9 +148,14 @@ class SandwichGatedBlock(Part):
                 f, slot_w = self.ffn.forward_slots(b)
             else:
                 f, slot_w = self.ffn.forward(b), None
-            g = linear(b, self.w_g2)
+            g = linear(b, self.w_g2) if self.gated else None
             normed = ops.gated_postnorm_add(x, x, f, g, self.b_g2, n3.weight, n3.eps, slot_weights=slot_w,
                                             next_weight=nxt_w, next_eps=nxt_eps, depth=depth)
         if self.depth_levels:
             x = stream
         return x, (NormedRows(normed, nxt_w, nxt_eps) if normed is not None and nxt_w is not None else None)
+
+
+@register_part("block", "sandwich")
+class SandwichBlock(SandwichGatedBlock):
+    gated = False

@@ -77,3 +77,39 @@ class GatedMLP(FeedForward):
             gate_up = linear(x, self.w_gate_up)                   # [T, 2I]
             ops.silu_mul(gate_up, act)
         return linear(act, self.w_down, residual=residual)
+
+
+@register_part("feed_forward", "plain_mlp")
+class PlainMLP(FeedForward):
+    """down(act(up(x))): two matrices, no gate and no bias; the activation is float32 arithmetic on the
+    first product's result.
+
+    params: hidden_size, intermediate_size, activation ("relu_squared": max(z, 0)^2, "silu", "gelu_tanh"),
+    tensor_names (keys "up", "down")."""
+    graph_safe = True
+
+    def __init__(self, spec: PartSpec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        self.hidden = int(spec["hidden_size"])
+        self.inter = int(spec["intermediate_size"])
+        self.activation = str(spec["activation"])
+        if self.activation not in ops.PLAIN_ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r}; known: {sorted(ops.PLAIN_ACTIVATIONS)}")
+        names = dict(spec.get().get("tensor_names") or ())
+        if sorted(names) != ["down", "up"]:
+            raise ValueError("a plain_mlp spec names its weights: tensor_names with the keys up, down")
+        self.names = {k: prefix + str(v) for k, v in names.items()}
+        self.w_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(self.names["up"], (self.inter, self.hidden)),
+                TensorSpec(self.names["down"], (self.hidden, self.inter))]
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        self.w_up, self.w_down = tensors[self.names["up"]], tensors[self.names["down"]]
+
+    def forward(self, x):
+        u = linear(x, self.w_up)
+        ops.act(u, u, self.activation)
+        return linear(u, self.w_down)

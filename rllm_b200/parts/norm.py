@@ -19,7 +19,9 @@ from .spec import PartSpec, TensorSpec
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Norm):
-    """params: size, eps, name (tensor name below the prefix)."""
+    """params: size, eps, name (tensor name below the prefix), unit_offset (True: the file stores the
+    weight's distance from one, y = x / rms * (1 + w); the sum is taken once, in float32, when the
+    weights are loaded, and the kernels see an ordinary weight)."""
     graph_safe = True
 
     def __init__(self, spec: PartSpec, prefix: str = ""):
@@ -27,13 +29,16 @@ class RMSNorm(Norm):
         self.size = int(spec["size"])
         self.eps = float(spec["eps"])
         self.name = prefix + str(spec["name"])
+        self.unit_offset = bool(spec.get().get("unit_offset", False))
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(self.name, (self.size,), role="vector", init=("one_plus_normal", 0.1))]
+        init = ("normal", 0.1) if self.unit_offset else ("one_plus_normal", 0.1)
+        return [TensorSpec(self.name, (self.size,), role="vector", init=init)]
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors[self.name]
+        w = tensors[self.name]
+        self.weight = (1.0 + w.float()).contiguous() if self.unit_offset else w
 
     def forward(self, x: torch.Tensor, act_dtype: torch.dtype) -> torch.Tensor:
         out = torch.empty(x.shape, dtype=act_dtype, device=x.device)

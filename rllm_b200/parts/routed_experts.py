@@ -22,8 +22,13 @@ largest of s + c are chosen, c a stored vector [experts] that only the choice se
 its result is added, multiplied by sigmoid(w . x) with one stored row w [1, hidden]
 (tensor name "shared_gate") if that name is given.
 
+With score "softmax" two more options.  ``groups`` = (count, keep): the experts form ``count``
+equal groups of neighbours; a group's score is the largest score in it, and only experts of the
+``keep`` groups with the largest scores (lowest index among equals) can be chosen.
+``renormalise`` True: the chosen experts' scores are divided by their sum (+ 1e-20).
+
 params: hidden_size, inner_size, num_experts, top, limit, alpha, up_shift, score
-("softmax" if absent), route_scale (1), shared (None),
+("softmax" if absent), route_scale (1), shared (None), groups (None), renormalise (False),
 tensor_names (keys "router", "gate", "up", "down"; the last three with ``{e}`` where
 the expert's number stands; optional "correction", "shared_gate").
 """
@@ -58,6 +63,15 @@ class RoutedExperts(FeedForward):
         if self.score not in ("softmax", "sigmoid"):
             raise ValueError(f"score {self.score!r}; known: softmax, sigmoid")
         self.route_scale = float(p.get("route_scale") if p.get("route_scale") is not None else 1.0)
+        g = p.get("groups")
+        self.groups, self.keep = (int(g[0]), int(g[1])) if g else (0, 0)
+        self.renormalise = bool(p.get("renormalise", False))
+        if g and (self.score != "softmax" or self.groups < 1 or self.experts % self.groups or
+                  not 1 <= self.keep <= self.groups or self.keep * (self.experts // self.groups) < self.top):
+            raise ValueError(f"groups {tuple(g)}: with score 'softmax', count divides the {self.experts} experts and "
+                             f"the kept groups hold at least top = {self.top} experts")
+        if self.renormalise and self.score != "softmax":
+            raise ValueError("renormalise goes with score 'softmax'")
         names = dict(p.get("tensor_names") or ())
         if not {"down", "gate", "router", "up"} <= set(names) or \
                 set(names) - {"down", "gate", "router", "up", "correction", "shared_gate"}:
@@ -110,7 +124,7 @@ class RoutedExperts(FeedForward):
         if self.score == "sigmoid":
             ids, scores = ops.moe_choose_sigmoid(logits, self.top, self.correction, self.route_scale)
         else:
-            ids, scores = ops.moe_choose(logits, self.top)
+            ids, scores = ops.moe_choose(logits, self.top, self.groups, self.keep, self.renormalise)
         return ops.moe_experts(x, ids, self.w_gate_up, self.w_down, self.limit, self.alpha, self.up_shift), scores
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
