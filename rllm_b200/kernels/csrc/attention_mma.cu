@@ -35,6 +35,8 @@
 //   gate        a row of gate pre-activations per token: the result is multiplied by sigmoid(gate[h])
 //               (gate_mode 1, one number a head) or sigmoid(gate[h * d + i]) (gate_mode 2, one an element).
 // The plain forms are compiled without any of it.
+//   slopes      float32 [nq]: slopes[h] * (query position - key position) is taken off the scaled (and capped)
+//               score: a bias linear in the distance;
 //   bias, mag   (decode form, with the rotation and the cache write fused in) float32 [nq d + nkv d + nkv d]
 //               added to the token's q, k and v ahead of the rotation; cosine and sine times mag.
 struct AttnOpts {
@@ -45,8 +47,9 @@ struct AttnOpts {
   int gate_stride, gate_mode;
   const float* bias;
   float mag;
+  const float* slopes;
 };
-#define ATTN_NO_OPTS AttnOpts{0, 0, 0.f, nullptr, nullptr, 0, 0, nullptr, 1.f}
+#define ATTN_NO_OPTS AttnOpts{0, 0, 0.f, nullptr, nullptr, 0, 0, nullptr, 1.f, nullptr}
 
 #define BM 64          // rows per CTA (prefill)
 #define BN 64          // keys per tile
@@ -199,13 +202,27 @@ template <int DT, int NT, bool OPT = false>
 __device__ __forceinline__ void softmax_tile(float (*s)[4], float (*o)[4], float* m, float* l, int j0,
                                              const int* row_lo, const int* row_hi, float scale_log2,
                                              int lane, const int* row_keep = nullptr, float cap_a = 0.f,
-                                             float cap_b = 0.f) {
+                                             float cap_b = 0.f, const float* row_slope = nullptr) {
   if (OPT && cap_b > 0.f) {
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
       for (int e = 0; e < 4; ++e)
         s[nt][e] = fmaf(-2.0f * cap_b, rcp_approx(ex2_approx(s[nt][e] * (cap_a * 2.8853900817779268f)) + 1.0f), cap_b);
+    scale_log2 = 1.0f;
+  }
+  if (OPT && row_slope != nullptr) {
+    // the distance bias: row_slope[h] (slope * log2 e) times (the row's position - the key's) comes off the
+    // scaled score; the row's position is row_hi - 1.  What it leaves at masked places is masked below.
+    const int col0 = (lane & 3) * 2;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int hrow = e >> 1;
+        const int j = j0 + nt * 8 + col0 + (e & 1);
+        s[nt][e] = fmaf(s[nt][e], scale_log2, -row_slope[hrow] * (float)(row_hi[hrow] - 1 - j));
+      }
     scale_log2 = 1.0f;
   }
   bool whole = j0 >= row_lo[0] && j0 + NT * 8 <= row_hi[0] && j0 >= row_lo[1] && j0 + NT * 8 <= row_hi[1];
@@ -343,11 +360,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
 
   // this thread's two rows
   int row_lo[2], row_hi[2], row_keep[2];
+  float row_slope[2] = {0.f, 0.f};
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = warp * 16 + (lane >> 2) + h * 8;
     const int tl = r / g;
     row_keep[h] = keep;
+    if (OPT && opt.slopes) row_slope[h] = opt.slopes[kvh * g + (r - tl * g)] * 1.4426950408889634f;
     if (tl < ntok) {
       const int p = pos0 + t0 + tl;
       row_hi[h] = p + 1;
@@ -393,7 +412,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restr
     }
     float sc[8][4];
     qk_tile<D, 8>(sc, qf, sK + stage * BN * D, lane);
-    softmax_tile<D / 8, 8, OPT>(sc, o, m, l, kt * BN, row_lo, row_hi, scale_log2, lane, row_keep, cap_a, cap_b);
+    softmax_tile<D / 8, 8, OPT>(sc, o, m, l, kt * BN, row_lo, row_hi, scale_log2, lane, row_keep, cap_a, cap_b,
+                                (OPT && opt.slopes) ? row_slope : nullptr);
     pv_tile<D, 8>(o, sc, sV + stage * BN * D, lane);
     __syncthreads();
   }
@@ -683,12 +703,14 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
     for (int kk = 0; kk < D / 16; ++kk)
       ldmatrix_x4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], tile_ptr<D>(sQ, lane & 15, kk * 2 + (lane >> 4)));
     int row_lo[2], row_hi[2], row_keep[2];
+    float row_slope[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       const int r = (lane >> 2) + h * 8;
       row_lo[h] = kmin;
       row_hi[h] = r < g ? len : 0;
       row_keep[h] = kept;
+      row_slope[h] = (OPT && opt.slopes && r < g) ? opt.slopes[kvh * g + r] * 1.4426950408889634f : 0.f;
     }
     const float cap_a = (OPT && opt.softcap > 0.f) ? scale_log2 * 0.6931471805599453f / opt.softcap : 0.f;
     const float cap_b = (OPT && opt.softcap > 0.f) ? opt.softcap * 1.4426950408889634f : 0.f;
@@ -723,7 +745,8 @@ attention_decode_kernel(bf16* __restrict__ qkv, int q_stride, bf16* __restrict__
       }
       float sc[TBN / 8][4];
       qk_tile<D, TBN / 8>(sc, qf, sK, lane);
-      softmax_tile<D / 8, TBN / 8, OPT>(sc, o, m, l, j0, row_lo, row_hi, scale_log2, lane, row_keep, cap_a, cap_b);
+      softmax_tile<D / 8, TBN / 8, OPT>(sc, o, m, l, j0, row_lo, row_hi, scale_log2, lane, row_keep, cap_a, cap_b,
+                                        (OPT && opt.slopes) ? row_slope : nullptr);
       pv_tile<D, TBN / 8>(o, sc, sV, lane);
       __syncwarp();                // every lane is through with this stage
       issue(t + STAGES);
@@ -945,11 +968,11 @@ RLLM_EXPORT int rllm_attention_prefill_bf16_opts(const void* q, int q_stride, vo
                                                  int seq_end, int num_tokens, int nq, int nkv, int d, int page_size,
                                                  int num_pages, int window, float scale, int keep_first, int chunk,
                                                  float softcap, const float* sinks, const void* gate, int gate_stride,
-                                                 int gate_mode, int* err, cudaStream_t stream) {
+                                                 int gate_mode, const float* slopes, int* err, cudaStream_t stream) {
   if (check_opts(window, keep_first, chunk, softcap, gate, gate_stride, gate_mode)) return RLLM_E_BADARG;
   return prefill_bf16<true>(q, q_stride, out, kcache, vcache, block_table, max_blocks, q_start, seq_lens, seq_begin,
                             seq_end, num_tokens, nq, nkv, d, page_size, num_pages, window, scale, err, stream,
-                            AttnOpts{keep_first, chunk, softcap, sinks, (const bf16*)gate, gate_stride, gate_mode, nullptr, 1.f});
+                            AttnOpts{keep_first, chunk, softcap, sinks, (const bf16*)gate, gate_stride, gate_mode, nullptr, 1.f, slopes});
 }
 
 // floats of workspace that a decode call with these sizes needs
@@ -1088,14 +1111,14 @@ RLLM_EXPORT int rllm_attention_decode_bf16_opts(void* q, int q_stride, void* out
                                                 int num_pages, int window, float scale, int keep_first, int chunk,
                                                 float softcap, const float* sinks, const void* gate, int gate_stride,
                                                 int gate_mode, const double* inv_freq, int rotary_dim, int write_kv,
-                                                const float* bias, float mag, float* workspace, int* counters,
-                                                int* err, cudaStream_t stream) {
+                                                const float* bias, float mag, const float* slopes, float* workspace,
+                                                int* counters, int* err, cudaStream_t stream) {
   if (check_opts(window, keep_first, chunk, softcap, gate, gate_stride, gate_mode)) return RLLM_E_BADARG;
   if (bias && !write_kv) return RLLM_E_BADARG;       // (the biases belong to the step that writes the token's key)
   return decode_bf16<true>(q, q_stride, out, kcache, vcache, block_table, max_blocks, seq_lens, num_seqs, max_seq_len,
                            nq, nkv, d, page_size, num_pages, window, scale, inv_freq, rotary_dim, write_kv, workspace,
                            counters, err, stream, false,
-                           AttnOpts{keep_first, chunk, softcap, sinks, (const bf16*)gate, gate_stride, gate_mode, bias, mag});
+                           AttnOpts{keep_first, chunk, softcap, sinks, (const bf16*)gate, gate_stride, gate_mode, bias, mag, slopes});
 }
 
 // ---------------------------------------------------------------------------

@@ -143,6 +143,7 @@ struct AtOpts {
   const float* sinks;
   const bf16* gate;
   int gate_stride, gate_mode;
+  const float* slopes;          // float32 [nq] or null: slopes[h] * (query position - key position) comes off the score
 };
 
 // Q, two stages of K and of V, barriers: two CTAs fit one SM
@@ -378,7 +379,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const bool capped = OPT && opt.softcap > 0.f;
     // capped scores: cap * log2 e * tanh(s * scale / cap), tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1)
     const float cap_a = capped ? scale_log2 * 2.0f / opt.softcap : 0.f, cap_b = capped ? opt.softcap * 1.4426950408889634f : 0.f;
-    const float sl2 = capped ? 1.0f : scale_log2;
+    // a bias linear in the distance: the scaled (capped) score minus slope * log2 e * (pos - key), made here, so
+    // that the exponent below takes the scores as they are
+    const bool sloped = OPT && opt.slopes != nullptr;
+    const float slope2 = sloped ? opt.slopes[min(kvh * g + hl, nq - 1)] * 1.4426950408889634f : 0.f;
+    const float pre2 = capped ? 1.0f : scale_log2;
+    const float sl2 = (capped || sloped) ? 1.0f : scale_log2;
     float m_ref = -INFINITY, l = 0.f;
     const unsigned lane_sel = (unsigned)(quarter * 32) << 16;
     const int ntiles = num_tiles;
@@ -407,6 +413,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
       if (capped) {
 #pragma unroll
         for (int j = 0; j < HC; ++j) sc[j] = fmaf(-2.0f * cap_b, rcp_approx(at_ex2(sc[j] * cap_a) + 1.0f), cap_b);
+      }
+      if (sloped) {
+        const float off = -slope2 * (float)(pos - j0 - half * HC);      // key j of this thread lies (pos - j0 - half HC - j) back
+#pragma unroll
+        for (int j = 0; j < HC; ++j) sc[j] = fmaf(sc[j], pre2, fmaf(slope2, (float)j, off));
       }
       if (!(j0 >= clear_lo && j0 + AT_BN <= clear_hi)) {
         const unsigned lo_rel = (unsigned)(row_lo - j0 - half * HC), span = (unsigned)(row_hi - row_lo);
@@ -662,7 +673,7 @@ RLLM_EXPORT int rllm_attention_prefill_tcgen05(const void* q, int q_stride, int 
                                                cudaStream_t stream) {
   return at_prefill<false>(q, q_stride, num_q_rows, out, kcache, vcache, block_table, max_blocks, q_start, seq_lens,
                            seq_begin, seq_end, num_tokens, nq, nkv, d, page_size, num_pages, window, scale, err, stream,
-                           AtOpts{0, 0, 0.f, nullptr, nullptr, 0, 0});
+                           AtOpts{0, 0, 0.f, nullptr, nullptr, 0, 0, nullptr});
 }
 
 // The same with the options of the head comment; gate [num_q_rows, gate_stride], a row per row of q.
@@ -672,12 +683,12 @@ RLLM_EXPORT int rllm_attention_prefill_tcgen05_opts(const void* q, int q_stride,
                                                     int seq_begin, int seq_end, int num_tokens, int nq, int nkv, int d,
                                                     int page_size, int num_pages, int window, float scale,
                                                     int keep_first, int chunk, float softcap, const float* sinks,
-                                                    const void* gate, int gate_stride, int gate_mode, int* err,
-                                                    cudaStream_t stream) {
+                                                    const void* gate, int gate_stride, int gate_mode,
+                                                    const float* slopes, int* err, cudaStream_t stream) {
   if (keep_first < 0 || chunk < 0 || !(softcap >= 0.f) || gate_mode < 0 || gate_mode > 2 || (gate_mode && !gate) ||
       (keep_first > 0 && window <= 0) || (gate_mode && gate_stride <= 0))
     return RLLM_E_BADARG;
   return at_prefill<true>(q, q_stride, num_q_rows, out, kcache, vcache, block_table, max_blocks, q_start, seq_lens,
                           seq_begin, seq_end, num_tokens, nq, nkv, d, page_size, num_pages, window, scale, err, stream,
-                          AtOpts{keep_first, chunk, softcap, sinks, (const bf16*)gate, gate_stride, gate_mode});
+                          AtOpts{keep_first, chunk, softcap, sinks, (const bf16*)gate, gate_stride, gate_mode, slopes});
 }

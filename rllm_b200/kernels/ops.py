@@ -470,20 +470,21 @@ def attention_prefill_bf16(q: torch.Tensor, q_stride: int, out: torch.Tensor, kc
                            seq_lens: torch.Tensor, seq_begin: int, seq_end: int, num_tokens: int, nq: int,
                            nkv: int, d: int, window: int, scale: float, err: torch.Tensor, keep_first: int = 0,
                            chunk: int = 0, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None,
-                           gate: Optional[torch.Tensor] = None, gate_per_head: bool = False) -> None:
+                           gate: Optional[torch.Tensor] = None, gate_per_head: bool = False,
+                           slopes: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention of the prompt portions of sequences seq_begin .. seq_end-1.  ``keep_first``,
-    ``chunk``, ``softcap``, ``sinks`` and ``gate`` as in ``attention_simt_kv`` (gate: a row per row of q)."""
+    ``chunk``, ``softcap``, ``sinks``, ``gate`` and ``slopes`` as in ``attention_simt_kv`` (gate: a row per row of q)."""
     lib = build.load_library("attention_mma")
     _contig(out, "out"); _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
     assert q.dtype is torch.bfloat16 and kcache.dtype is torch.bfloat16 and out.dtype is torch.bfloat16
-    if keep_first or chunk or softcap or sinks is not None or gate is not None:
-        gate_mode = _attention_opts_asserts(sinks, gate, gate_per_head, nq, d)
+    if keep_first or chunk or softcap or sinks is not None or gate is not None or slopes is not None:
+        gate_mode = _attention_opts_asserts(sinks, gate, gate_per_head, nq, d, slopes)
         _check(lib.rllm_attention_prefill_bf16_opts(
             _ptr(q), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_table),
             c_int(block_table.shape[1]), _ptr(q_start), _ptr(seq_lens), c_int(seq_begin), c_int(seq_end),
             c_int(num_tokens), c_int(nq), c_int(nkv), c_int(d), c_int(kcache.shape[2]), c_int(kcache.shape[0]),
             c_int(window), c_float(scale), c_int(keep_first), c_int(chunk), c_float(softcap), _ptr(sinks), _ptr(gate),
-            c_int(gate.stride(0) if gate is not None else 0), c_int(gate_mode), _ptr(err), _stream()),
+            c_int(gate.stride(0) if gate is not None else 0), c_int(gate_mode), _ptr(slopes), _ptr(err), _stream()),
             "attention_prefill_bf16_opts")
         return
     _check(lib.rllm_attention_prefill_bf16(_ptr(q), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache),
@@ -507,21 +508,22 @@ def attention_prefill_tcgen05(q: torch.Tensor, q_stride: int, out: torch.Tensor,
                               seq_lens: torch.Tensor, seq_begin: int, seq_end: int, num_tokens: int, nq: int,
                               nkv: int, d: int, window: int, scale: float, err: torch.Tensor, keep_first: int = 0,
                               chunk: int = 0, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None,
-                              gate: Optional[torch.Tensor] = None, gate_per_head: bool = False) -> None:
+                              gate: Optional[torch.Tensor] = None, gate_per_head: bool = False,
+                              slopes: Optional[torch.Tensor] = None) -> None:
     """Attention of the prompt portions of sequences seq_begin .. seq_end-1 on the
     tcgen05 tensor cores (same contract and options as ``attention_prefill_bf16``; ``q`` is the
     first of ``q.shape[0]`` rows of ``q_stride`` elements)."""
     lib = build.load_library("attention_tcgen05")
     _contig(out, "out"); _contig(kcache, "kcache"); _contig(vcache, "vcache"); _contig(block_table, "block_table")
     assert q.dtype is torch.bfloat16 and kcache.dtype is torch.bfloat16 and out.dtype is torch.bfloat16
-    if keep_first or chunk or softcap or sinks is not None or gate is not None:
-        gate_mode = _attention_opts_asserts(sinks, gate, gate_per_head, nq, d)
+    if keep_first or chunk or softcap or sinks is not None or gate is not None or slopes is not None:
+        gate_mode = _attention_opts_asserts(sinks, gate, gate_per_head, nq, d, slopes)
         _check(lib.rllm_attention_prefill_tcgen05_opts(
             _ptr(q), c_int(q_stride), c_int(q.shape[0]), _ptr(out), _ptr(kcache), _ptr(vcache), _ptr(block_table),
             c_int(block_table.shape[1]), _ptr(q_start), _ptr(seq_lens), c_int(seq_begin), c_int(seq_end),
             c_int(num_tokens), c_int(nq), c_int(nkv), c_int(d), c_int(kcache.shape[2]), c_int(kcache.shape[0]),
             c_int(window), c_float(scale), c_int(keep_first), c_int(chunk), c_float(softcap), _ptr(sinks), _ptr(gate),
-            c_int(gate.stride(0) if gate is not None else 0), c_int(gate_mode), _ptr(err), _stream()),
+            c_int(gate.stride(0) if gate is not None else 0), c_int(gate_mode), _ptr(slopes), _ptr(err), _stream()),
             "attention_prefill_tcgen05_opts")
         return
     _check(lib.rllm_attention_prefill_tcgen05(_ptr(q), c_int(q_stride), c_int(q.shape[0]), _ptr(out), _ptr(kcache),
@@ -536,8 +538,10 @@ _decode_counters = {}
 _retired_counters = []          # buffers that grew out of use: captured graphs may still hold their address
 
 
-def _attention_opts_asserts(sinks, gate, gate_per_head: bool, nq: int, d: int) -> int:
+def _attention_opts_asserts(sinks, gate, gate_per_head: bool, nq: int, d: int, slopes=None) -> int:
     """Checks of the tensor-core kernels' options; returns the kernels' gate mode."""
+    if slopes is not None:
+        assert slopes.dtype is torch.float32 and slopes.numel() == nq and slopes.is_contiguous()
     if sinks is not None:
         assert sinks.dtype is torch.float32 and sinks.numel() == nq and sinks.is_contiguous()
     if gate is None:
@@ -571,7 +575,7 @@ def attention_decode_bf16(qkv: torch.Tensor, q_stride: int, out: torch.Tensor, k
                           write_kv: bool = False, keep_first: int = 0, chunk: int = 0, softcap: float = 0.0,
                           sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
                           gate_per_head: bool = False, bias: Optional[torch.Tensor] = None,
-                          magnitude: float = 1.0) -> None:
+                          magnitude: float = 1.0, slopes: Optional[torch.Tensor] = None) -> None:
     """Split-KV tensor-core attention of sequences 0 .. num_seqs-1, one query token
     each: row s of ``qkv`` holds the token's q heads (and behind them its k and v
     heads if ``write_kv``), row s of ``out`` gets the result.  ``rotary_dim`` > 0
@@ -592,8 +596,9 @@ def attention_decode_bf16(qkv: torch.Tensor, q_stride: int, out: torch.Tensor, k
     if rotary_dim:
         assert inv_freq is not None and inv_freq.dtype is torch.float64 and inv_freq.numel() == rotary_dim // 2
     counters = _counters_for(qkv.device, num_seqs * nkv)
-    if keep_first or chunk or softcap or sinks is not None or gate is not None or bias is not None or magnitude != 1.0:
-        gate_mode = _attention_opts_asserts(sinks, gate, gate_per_head, nq, d)
+    if keep_first or chunk or softcap or sinks is not None or gate is not None or bias is not None or \
+            magnitude != 1.0 or slopes is not None:
+        gate_mode = _attention_opts_asserts(sinks, gate, gate_per_head, nq, d, slopes)
         if bias is not None:
             assert write_kv and bias.dtype is torch.float32 and bias.is_contiguous() and bias.numel() == (nq + 2 * nkv) * d
         _check(lib.rllm_attention_decode_bf16_opts(
@@ -602,7 +607,7 @@ def attention_decode_bf16(qkv: torch.Tensor, q_stride: int, out: torch.Tensor, k
             c_int(d), c_int(kcache.shape[2]), c_int(kcache.shape[0]), c_int(window), c_float(scale), c_int(keep_first),
             c_int(chunk), c_float(softcap), _ptr(sinks), _ptr(gate), c_int(gate.stride(0) if gate is not None else 0),
             c_int(gate_mode), _ptr(inv_freq if rotary_dim else None), c_int(rotary_dim), c_int(1 if write_kv else 0),
-            _ptr(bias), c_float(magnitude), _ptr(workspace), _ptr(counters), _ptr(err), _stream()),
+            _ptr(bias), c_float(magnitude), _ptr(slopes), _ptr(workspace), _ptr(counters), _ptr(err), _stream()),
             "attention_decode_bf16_opts")
         return
     _check(lib.rllm_attention_decode_bf16(_ptr(qkv), c_int(q_stride), _ptr(out), _ptr(kcache), _ptr(vcache),
@@ -622,11 +627,6 @@ def attention_decode_workspace(num_seqs: int, nq: int, d: int, max_seq_len: int)
 
 def mma_attention_takes(nq: int, nkv: int, d: int) -> bool:
     return d in (16, 32, 64, 128) and nq % nkv == 0 and nq // nkv <= 16
-
-
-def mma_attention_takes_opts(opts: dict) -> bool:
-    """Whether the tensor-core attention kernels have every option of ``opts`` (the CUDA-core kernel has all)."""
-    return opts.get("slopes") is None
 
 
 def use_mma_attention(dtype: torch.dtype, nq: int, nkv: int, d: int) -> bool:

@@ -264,8 +264,7 @@ class PagedAttention(Mixer):
                     gate_per_head=self.gate == "head") if self.masked else {}
         if self.slopes is not None:
             opts["slopes"] = self.slopes
-        if dv == d and d % 16 == 0 and ops.use_mma_attention(qkv.dtype, self.nq, self.nkv, d) and \
-                ops.mma_attention_takes_opts(opts):
+        if dv == d and d % 16 == 0 and ops.use_mma_attention(qkv.dtype, self.nq, self.nkv, d):
             nd = ctx.num_decode
             if nd:
                 fused = dict(inv_freq=inv_freq, rotary_dim=rd, write_kv=True, bias=self.b_qkv, magnitude=mag) \

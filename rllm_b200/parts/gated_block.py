@@ -153,6 +153,9 @@ class SandwichGatedBlock(Part):
                                             next_weight=nxt_w, next_eps=nxt_eps, depth=depth)
         if self.depth_levels:
             x = stream
+        trace = ctx.extras.get("residual_trace")         # a list: the stream after every layer (a copy)
+        if trace is not None:
+            trace.append(x.clone())
         return x, (NormedRows(normed, nxt_w, nxt_eps) if normed is not None and nxt_w is not None else None)
 
 

@@ -159,12 +159,15 @@ def latent_attention(w, pre: str, m: dict, h: torch.Tensor, eps: float) -> torch
 def mlstm(w, pre: str, m: dict, h: torch.Tensor, eps: float) -> torch.Tensor:
     """The matrix memory, token by token."""
     T, H, d, dv = h.shape[0], int(m["heads"]), int(m["dim"]), int(m["vdim"])
-    cap = float(m["gate_cap"])
+    cap = float(m.get("gate_cap") or 0.0)
+
+    def capped(z):
+        return cap * torch.tanh(z / cap) if cap else z
     q = (h @ w[pre + "q"].t()).view(T, H, d) * d ** -0.5
     k = (h @ w[pre + "k"].t()).view(T, H, d)
     v = (h @ w[pre + "v"].t()).view(T, H, dv)
-    gi = cap * torch.tanh((h @ w[pre + "i"].t() + w[pre + "i.b"]) / cap)                       # [T, H]
-    gf = torch.nn.functional.logsigmoid(cap * torch.tanh((h @ w[pre + "f"].t() + w[pre + "f.b"]) / cap))
+    gi = capped(h @ w[pre + "i"].t() + w[pre + "i.b"])                                         # [T, H]
+    gf = torch.nn.functional.logsigmoid(capped(h @ w[pre + "f"].t() + w[pre + "f.b"]))
     S = torch.zeros(H, d, dv, dtype=F64)
     n = torch.zeros(H, d, dtype=F64)
     mx = torch.zeros(H, dtype=F64)
