@@ -476,6 +476,44 @@ MUNUPEL_SIZES = {
 }
 
 
+def tibelix(layers, width, mheads, mdim, mvdim, heads, kv_heads, dim, lheads, ldim, lrot, lvdim, q_rank, kv_rank,
+            experts, top, groups, keep, ff, shared, dense, vocab):
+    """layers of the pattern [mLSTM + dense, attention + experts, latent attention + experts, attention that
+    reads the second layer's keys and values + experts]: sandwich layers (a norm before and after each sublayer)."""
+    moe = {"kind": "moe", "expert": {"ff": ff}, "shared": {"ff": shared},
+           "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+           "q_temp": {"coef": 0.5, "every": 64}}
+    lat = {"heads": lheads, "dim": ldim, "rot_dim": lrot, "vdim": lvdim, "q_rank": q_rank, "kv_rank": kv_rank,
+           "scale": (ldim + lrot) ** -0.5,
+           "rot": {"base": 250000.0, "dims": lrot, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    out = []
+    for i in range(layers):
+        k = i % 4
+        if k == 0:
+            out.append({"type": "mlstm", "mixer": {"heads": mheads, "dim": mdim, "vdim": mvdim, "gate_cap": 15.0},
+                        "mlp": {"kind": "dense", "ff": dense}})
+        elif k == 2:
+            out.append({"type": "latent_attention", "mixer": lat, "mlp": moe})
+        else:
+            out.append({"type": "attention", "mixer": dict(att, kv_from=i - 2) if k == 3 else att, "mlp": moe})
+    return {"architecture": "Tibelix", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "max_positions": 8192,
+            "layers": out}
+
+
+# Tibelix beside Fasulix (the closest design: latent attention, a recurrence with state slots and routed experts
+# in layers with a norm before and after each sublayer) of equal width, layers, vocabulary, experts and expert
+# width, and the Llama of that width.
+TIBELIX_SIZES = {
+    "w1024": dict(layers=4, width=1024, mheads=8, mdim=64, mvdim=128, heads=16, kv_heads=4, dim=64, lheads=8, ldim=64,
+                  lrot=32, lvdim=64, q_rank=384, kv_rank=256, experts=16, top=2, groups=4, keep=2, ff=1024, shared=1024,
+                  dense=2048, vocab=32768),
+    "w2048": dict(layers=4, width=2048, mheads=8, mdim=128, mvdim=256, heads=16, kv_heads=4, dim=128, lheads=16,
+                  ldim=128, lrot=64, lvdim=128, q_rank=768, kv_rank=512, experts=32, top=4, groups=8, keep=4, ff=1024,
+                  shared=2048, dense=4096, vocab=32768),
+}
+
+
 def compare_designs(args):
     """Prefill and decode throughput of Fasulix at sizes that resemble a real model's layers (random weights)
     beside the Llama of equal size, through the same step function; and, from one eager prefill step and one
@@ -548,8 +586,15 @@ def compare_designs(args):
             return 0.0, a[0].numel() * 4.0 + a[0][0].numel() * 2.0
         if name == "streams_write":
             return 0.0, a[0].numel() * 8.0 + a[0][0].numel() * 4.0
-        if name in ("head_norm_kv_write", "act_mul"):
+        if name in ("head_norm_kv_write", "act_mul", "act", "sigmoid_gate"):
             return 0.0, 4.0 * a[0].numel()
+        if name == "mlstm_scan":
+            heads, d, dv = a[12], a[13], a[14]
+            # q, k, v in, o out (float32), the gates; the state once in and once out per sequence
+            return 4.0 * a[0].shape[0] * heads * d * dv, a[0].shape[0] * heads * (4.0 * d + 2.0 * dv + 4.0 * dv + 8.0) + \
+                8.0 * S * heads * (d * dv + d + 1)
+        if name == "head_gated_rmsnorm":
+            return 0.0, 8.0 * a[0].numel()
         if name in ("rms_mean2", "gated_rmsnorm"):
             return 0.0, 6.0 * a[0].numel()
         if name == "attention_simt_kv":
@@ -557,7 +602,7 @@ def compare_designs(args):
             vis, keys = seen(window, kw.get("keep_first", 0), kw.get("chunk", 0))
             return 2.0 * (dk + dv) * nq * vis, 2.0 * (keys * nkv * (dk + dv) + Tn * nq * (dk + dv))
         if name == "gated_postnorm_add":
-            return 0.0, 8.0 * a[0].numel() + 2.0 * (a[2].numel() + 2 * a[3].numel())
+            return 0.0, 8.0 * a[0].numel() + 2.0 * (a[2].numel() + (2 * a[3].numel() if a[3] is not None else a[0].numel()))
         if name == "depth_average":
             return 0.0, 4.0 * a[1] * a[0][0].numel() + 6.0 * a[0][0].numel()
         if name == "rmsnorm":
@@ -580,7 +625,8 @@ def compare_designs(args):
             "silu_mul", "latent_prep", "latent_q_rot", "rope_kv_write", "gemm_small_m", "moe_choose", "gemm_small_m_residual",
             "gemm_small_m_rstd", "gemm_tcgen05", "embedding", "lightning_scan", "selective_scan", "causal_conv",
             "streams_read", "streams_write", "head_norm_kv_write", "attention_simt_kv", "rms_mean2", "gated_rmsnorm",
-            "act_mul", "moe_choose_sigmoid", "weighted_slot_sum", "layernorm", "add_rows", "add_row_bias")]
+            "act_mul", "moe_choose_sigmoid", "weighted_slot_sum", "layernorm", "add_rows", "add_row_bias", "mlstm_scan",
+            "head_gated_rmsnorm", "act", "sigmoid_gate")]
         saved, log = {}, []
 
         def wrap(name, fn):
@@ -703,6 +749,8 @@ def compare_designs(args):
         row = {"size": name}
         if args.design == "fevolorn":
             row["fevolorn"] = measure("fevolorn", fevolorn(**FEVOLORN_SIZES[name]))
+        if args.design == "tibelix":
+            row["tibelix"] = measure("tibelix", tibelix(**TIBELIX_SIZES[name]))
         if args.design == "munupel":
             row["munupel"] = measure("munupel", munupel(**MUNUPEL_SIZES[name]))
         else:
@@ -735,7 +783,7 @@ def main():
     ap.add_argument("--no-standin", action="store_true", help="skip the library-operator stand-in")
     ap.add_argument("--settle-steps", type=int, default=SETTLE_STEPS,
                     help="untimed decode steps of a device-timed point before its warm-up steps (0 for a short capture under a profiler)")
-    ap.add_argument("--design", default=None, choices=["fasulix", "fevolorn", "munupel"],
+    ap.add_argument("--design", default=None, choices=["fasulix", "fevolorn", "munupel", "tibelix"],
                     help="instead of the default workload: this design beside the Llama of equal size (prefill and "
                          "decode throughput, kernels against their rooflines)")
     ap.add_argument("--design-size", default=None, help="only this entry of the design comparison's sizes")

@@ -16,8 +16,11 @@
 //   mlstm_scan           one warp per (sequence, head, 32 value columns): it walks the
 //                        sequence's tokens of this step in order with its slice of S in
 //                        shared memory and n in registers (every warp of a head carries n;
-//                        the first writes it back).  A token's arithmetic does not depend
-//                        on how the sequence was cut into steps or on the batch around it.
+//                        the first writes it back).  Long portions are cut into chunks of 64
+//                        tokens that run side by side: every chunk's end state from zero, then
+//                        the states at the chunks' starts chunk after chunk (an elementwise
+//                        pass), then every chunk's tokens from its start state.  Either way a
+//                        token's result is the recurrence's; the two ways differ by rounding.
 //   head_gated_rmsnorm   out = o / sqrt(mean_head(o^2) + eps) * w * sigmoid(g): the norm runs
 //                        over each head's dv values, w is [heads * dv]; one warp a (token, head).
 #include "common.cuh"
@@ -28,11 +31,21 @@
 __device__ __forceinline__ float ml_soft_cap(float z, float cap) { return cap > 0.f ? cap * tanhf(z / cap) : z; }
 __device__ __forceinline__ float ml_logsigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
 
-template <typename T>
+// MODE 0: a unit is a sequence: all its tokens of this step, from its state slot and back into it.
+// MODE 1: a unit is a chunk of ML_CHUNK tokens of a sequence: its end state from a zero state under a maximum of
+//         its own that starts at minus infinity (S, n, that maximum, and the sum of the chunk's log forget gates)
+//         goes to `local`; nothing else is written.
+// MODE 2: a unit is such a chunk, started from the state that `start` holds for it; outputs are written, and the
+//         sequence's last chunk writes the slot.
+// Units of MODE 1 and 2 are numbered sequence by sequence; a block finds its sequence by walking q_start.
+#define ML_CHUNK 64
+
+template <typename T, int MODE>
 __global__ void __launch_bounds__(32)
 mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* gates, const float* bias_i,
                   const float* bias_f, float cap, float qscale, float* state, const int* q_start, const int* slots,
-                  float* out, int heads, int d, int dv, int num_slots, int* err) {
+                  float* out, int num_seqs, int heads, int d, int dv, int num_slots, float* local, float* start,
+                  int* err) {
   pdl_wait();
   pdl_launch();
   extern __shared__ float sm[];          // S slice [d][32], then k [d], then q [d]
@@ -41,8 +54,26 @@ mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* g
   float* qs = ks + d;
   const int lane = threadIdx.x;
   const int j = blockIdx.x * 32 + lane;  // value column
-  const int h = blockIdx.y, s = blockIdx.z;
-  const int t0 = q_start[s], t1 = q_start[s + 1];
+  const int h = blockIdx.y;
+  int s = blockIdx.z, t0, t1, unit = blockIdx.z;
+  bool last_chunk = true;
+  if (MODE == 0) {
+    t0 = q_start[s];
+    t1 = q_start[s + 1];
+  } else {
+    int left = blockIdx.z;
+    s = -1;
+    for (int i = 0; i < num_seqs; ++i) {
+      const int n = (q_start[i + 1] - q_start[i] + ML_CHUNK - 1) / ML_CHUNK;
+      if (left < n) { s = i; break; }
+      left -= n;
+    }
+    if (s < 0) return;
+    t0 = q_start[s] + left * ML_CHUNK;
+    t1 = min(t0 + ML_CHUNK, q_start[s + 1]);
+    last_chunk = t1 == q_start[s + 1];
+    if (MODE == 1 && last_chunk) return;             // nobody reads the end state of a sequence's last chunk
+  }
   const int slot = slots[s];
   if (slot < 0 || slot >= num_slots) {
     if (lane == 0) atomicOr(err, 8);
@@ -50,33 +81,69 @@ mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* g
   }
   const size_t per_head = (size_t)d * dv + d + 1;
   float* st = state + ((size_t)slot * heads + h) * per_head;
+  // (MODE 2 reads every chunk's start state, the first one's too, from `start`: the slot is written by the
+  // sequence's last chunk, which may run at the same time)
+  const float* from = MODE == 2 ? start + ((size_t)unit * heads + h) * per_head : st;
   const bool live = j < dv;
-  for (int i = 0; i < d; ++i) S[i * 32 + lane] = live ? st[(size_t)i * dv + j] : 0.f;
   float n[ML_MAX_D / 32];
+  float m;
+  if (MODE == 1) {
+    for (int i = 0; i < d; ++i) S[i * 32 + lane] = 0.f;
 #pragma unroll
-  for (int r = 0; r < ML_MAX_D / 32; ++r) {
-    const int i = lane + 32 * r;
-    n[r] = i < d ? st[(size_t)d * dv + i] : 0.f;
+    for (int r = 0; r < ML_MAX_D / 32; ++r) n[r] = 0.f;
+    m = -INFINITY;
+  } else {
+    for (int i = 0; i < d; ++i) S[i * 32 + lane] = live ? from[(size_t)i * dv + j] : 0.f;
+#pragma unroll
+    for (int r = 0; r < ML_MAX_D / 32; ++r) {
+      const int i = lane + 32 * r;
+      n[r] = i < d ? from[(size_t)d * dv + i] : 0.f;
+    }
+    m = from[(size_t)d * dv + d];
   }
-  float m = st[(size_t)d * dv + d];
   const float bi = bias_i ? bias_i[h] : 0.f, bf = bias_f ? bias_f[h] : 0.f;
+  float bsum = 0.f;
+  // the next token's values are fetched while this token's are worked on
+  float nk[ML_MAX_D / 32], nq[ML_MAX_D / 32], nv = 0.f, nzi = 0.f, nzf = 0.f;
+  auto fetch = [&](int t) {
+    const T* qr = q + (size_t)t * stride + (size_t)h * d;
+    const T* kr = k + (size_t)t * stride + (size_t)h * d;
+#pragma unroll
+    for (int r = 0; r < ML_MAX_D / 32; ++r) {
+      const int i = lane + 32 * r;
+      if (i < d) { nk[r] = to_f32(kr[i]); if (MODE != 1) nq[r] = to_f32(qr[i]); }
+    }
+    nv = live ? to_f32(v[(size_t)t * stride + (size_t)h * dv + j]) : 0.f;
+    nzi = gates[(size_t)t * 2 * heads + h];
+    nzf = gates[(size_t)t * 2 * heads + heads + h];
+  };
+  if (t0 < t1) fetch(t0);
   for (int t = t0; t < t1; ++t) {
-    const float a = ml_soft_cap(gates[(size_t)t * 2 * heads + h] + bi, cap);
-    const float b = ml_logsigmoid(ml_soft_cap(gates[(size_t)t * 2 * heads + heads + h] + bf, cap));
+    const float a = ml_soft_cap(nzi + bi, cap);
+    const float b = ml_logsigmoid(ml_soft_cap(nzf + bf, cap));
     const float m_new = fmaxf(b + m, a);
     const float keep = expf(b + m - m_new), take = expf(a - m_new);
     m = m_new;
-    const T* qr = q + (size_t)t * stride + (size_t)h * d;
-    const T* kr = k + (size_t)t * stride + (size_t)h * d;
+    bsum += b;
     __syncwarp();
-    for (int i = lane; i < d; i += 32) { ks[i] = take * to_f32(kr[i]); qs[i] = to_f32(qr[i]) * qscale; }
-    const float vj = live ? to_f32(v[(size_t)t * stride + (size_t)h * dv + j]) : 0.f;
+#pragma unroll
+    for (int r = 0; r < ML_MAX_D / 32; ++r) {
+      const int i = lane + 32 * r;
+      if (i < d) { ks[i] = take * nk[r]; if (MODE != 1) qs[i] = nq[r] * qscale; }
+    }
+    const float vj = nv;
     __syncwarp();
+    if (t + 1 < t1) fetch(t + 1);
     float part = 0.f;
 #pragma unroll
     for (int r = 0; r < ML_MAX_D / 32; ++r) {
       const int i = lane + 32 * r;
-      if (i < d) { n[r] = fmaf(keep, n[r], ks[i]); part = fmaf(n[r], qs[i], part); }
+      if (i < d) { n[r] = fmaf(keep, n[r], ks[i]); if (MODE != 1) part = fmaf(n[r], qs[i], part); }
+    }
+    if (MODE == 1) {
+#pragma unroll 4
+      for (int i = 0; i < d; ++i) S[i * 32 + lane] = fmaf(keep, S[i * 32 + lane], ks[i] * vj);
+      continue;
     }
     const float dot = warp_sum(part);
     float num = 0.f;
@@ -89,40 +156,93 @@ mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* g
     const float den = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
     if (live) out[(size_t)t * heads * dv + (size_t)h * dv + j] = num / den;
   }
-  if (t1 > t0) {
-    if (live) for (int i = 0; i < d; ++i) st[(size_t)i * dv + j] = S[i * 32 + lane];
-    if (blockIdx.x == 0) {
+  if (t1 <= t0) return;
+  float* to = nullptr;
+  if (MODE == 0 || (MODE == 2 && last_chunk)) to = st;
+  if (MODE == 1) to = local + ((size_t)unit * heads + h) * (per_head + 1);
+  if (to == nullptr) return;
+  if (live) for (int i = 0; i < d; ++i) to[(size_t)i * dv + j] = S[i * 32 + lane];
+  if (blockIdx.x == 0) {
 #pragma unroll
-      for (int r = 0; r < ML_MAX_D / 32; ++r) {
-        const int i = lane + 32 * r;
-        if (i < d) st[(size_t)d * dv + i] = n[r];
-      }
-      if (lane == 0) st[(size_t)d * dv + d] = m;
+    for (int r = 0; r < ML_MAX_D / 32; ++r) {
+      const int i = lane + 32 * r;
+      if (i < d) to[(size_t)d * dv + i] = n[r];
     }
+    if (lane == 0) {
+      to[(size_t)d * dv + d] = m;
+      if (MODE == 1) to[(size_t)d * dv + d + 1] = bsum;
+    }
+  }
+}
+
+// Between the two chunked passes: from the chunks' local end states to the state at every chunk's start, chunk
+// after chunk.  With (X, m) the state at a chunk's start, (L, m', B) the chunk's local end state, its maximum and
+// the sum of its log forget gates:  m_end = max(m + B, m'),  X_end = exp(m + B - m_end) X + exp(m' - m_end) L.
+// One thread an element of a head's state; grid (elements / 256, heads, sequences).
+__global__ void __launch_bounds__(256)
+mlstm_chunk_starts_kernel(const float* state, const int* q_start, const int* slots, const float* local, float* start,
+                          int num_seqs, int heads, int d, int dv, int num_slots) {
+  pdl_wait();
+  pdl_launch();
+  const int s = blockIdx.z, h = blockIdx.y;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  const int per = d * dv + d;                       // S and n; the maximum lies behind them
+  int base = 0;
+  for (int i = 0; i < s; ++i) base += (q_start[i + 1] - q_start[i] + ML_CHUNK - 1) / ML_CHUNK;
+  const int nc = (q_start[s + 1] - q_start[s] + ML_CHUNK - 1) / ML_CHUNK;
+  const int slot = slots[s];
+  if (nc < 1 || slot < 0 || slot >= num_slots || e >= per) return;
+  const size_t per_head = (size_t)per + 1;
+  const float* st = state + ((size_t)slot * heads + h) * per_head;
+  float x = st[e], m = st[per];
+  for (int c = 0; c < nc; ++c) {
+    float* X = start + ((size_t)(base + c) * heads + h) * per_head;
+    X[e] = x;                                       // (the first chunk's start is the slot's state)
+    if (e == 0) X[per] = m;
+    if (c + 1 == nc) break;
+    const float* L = local + ((size_t)(base + c) * heads + h) * (per_head + 1);
+    const float ml = L[per], B = L[per + 1];
+    const float m_end = fmaxf(m + B, ml);
+    x = fmaf(expf(m + B - m_end), x, expf(ml - m_end) * L[e]);
+    m = m_end;
   }
 }
 
 // q, k: rows of heads * d; v: rows of heads * dv; all three with the row stride `stride` (views into one
 // product's result).  gates float32 [T, 2 heads]: the input gates' pre-activations, then the forget gates'.
 // state float32 [slots, heads, d * dv + d + 1]; out float32 [T, heads * dv].
+// chunks > 0 (the number of chunks of ML_CHUNK tokens over all sequences, each sequence cut from its first token
+// of this step) with workspaces local [chunks, heads, d * dv + d + 2] and start [chunks, heads, d * dv + d + 1]:
+// three launches that work on all chunks side by side; chunks == 0: one warp walks a sequence's tokens.
 RLLM_EXPORT int rllm_mlstm_scan(const void* q, const void* k, const void* v, int stride, int dtype, const float* gates,
                                 const float* bias_i, const float* bias_f, float cap, float qscale, float* state,
                                 const int* q_start, const int* slots, float* out, int num_seqs, int heads, int d,
-                                int dv, int num_slots, int* err, cudaStream_t stream) {
+                                int dv, int num_slots, int chunks, float* local, float* start, int* err,
+                                cudaStream_t stream) {
   if (num_seqs <= 0) return 0;
-  if (heads <= 0 || d <= 0 || dv <= 0 || num_slots <= 0 || !(cap >= 0.f)) return RLLM_E_BADARG;
-  if (d > ML_MAX_D || heads > 65535 || num_seqs > 65535) return RLLM_E_UNSUPPORTED;
+  if (heads <= 0 || d <= 0 || dv <= 0 || num_slots <= 0 || !(cap >= 0.f) || chunks < 0) return RLLM_E_BADARG;
+  if (chunks > 0 && (!local || !start)) return RLLM_E_BADARG;
+  if (d > ML_MAX_D || heads > 65535 || num_seqs > 65535 || chunks > 65535) return RLLM_E_UNSUPPORTED;
   const size_t smem = ((size_t)d * 32 + 2 * (size_t)d) * sizeof(float);
-  const dim3 grid((dv + 31) / 32, heads, num_seqs);
-#define ML_GO(T_)                                                                                             \
-  do {                                                                                                        \
-    if (smem > 48 * 1024)                                                                                     \
-      cudaFuncSetAttribute(mlstm_scan_kernel<T_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);    \
-    rllm_launch_pdl(mlstm_scan_kernel<T_>, grid, dim3(32), smem, stream, (const T_*)q, (const T_*)k,          \
-                    (const T_*)v, stride, gates, bias_i, bias_f, cap, qscale, state, q_start, slots, out,     \
-                    heads, d, dv, num_slots, err);                                                            \
+#define ML_GO(T_, MODE_, UNITS_)                                                                               \
+  do {                                                                                                         \
+    if (smem > 48 * 1024)                                                                                      \
+      cudaFuncSetAttribute(mlstm_scan_kernel<T_, MODE_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    rllm_launch_pdl(mlstm_scan_kernel<T_, MODE_>, dim3((dv + 31) / 32, heads, UNITS_), dim3(32), smem, stream,  \
+                    (const T_*)q, (const T_*)k, (const T_*)v, stride, gates, bias_i, bias_f, cap, qscale, state, \
+                    q_start, slots, out, num_seqs, heads, d, dv, num_slots, local, start, err);                \
   } while (0)
-  RLLM_DISPATCH_DTYPE(dtype, TT, ML_GO(TT));
+  if (chunks == 0) {
+    RLLM_DISPATCH_DTYPE(dtype, TT, ML_GO(TT, 0, num_seqs));
+  } else {
+    RLLM_DISPATCH_DTYPE(dtype, TT, ML_GO(TT, 1, chunks));
+    RLLM_LAUNCH_CHECK();
+    rllm_launch_pdl(mlstm_chunk_starts_kernel, dim3((d * dv + d + 255) / 256, heads, num_seqs), dim3(256), (size_t)0,
+                    stream, (const float*)state, q_start, slots, (const float*)local, start, num_seqs, heads, d, dv,
+                    num_slots);
+    RLLM_LAUNCH_CHECK();
+    RLLM_DISPATCH_DTYPE(dtype, TT, ML_GO(TT, 2, chunks));
+  }
 #undef ML_GO
   RLLM_LAUNCH_CHECK();
   return 0;

@@ -1402,14 +1402,22 @@ def mlstm_state_size(d: int, dv: int) -> int:
     return d * dv + d + 1
 
 
+MLSTM_CHUNK = 64               # tokens a chunk of the chunked scan (the kernel's ML_CHUNK)
+MLSTM_CHUNKED_FROM = 129       # a step whose longest portion has at least this many tokens scans in chunks
+
+
 def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gates: torch.Tensor, bias_i: torch.Tensor,
                bias_f: torch.Tensor, cap: float, qscale: float, state: torch.Tensor, q_start: torch.Tensor,
-               slots: torch.Tensor, num_seqs: int, heads: int, d: int, dv: int, err: torch.Tensor) -> torch.Tensor:
+               slots: torch.Tensor, num_seqs: int, heads: int, d: int, dv: int, err: torch.Tensor,
+               q_lens=None) -> torch.Tensor:
     """The mLSTM recurrence over this step's tokens of every sequence, in order, from and into the sequences'
     state slots.  q, k [T, heads * d] and v [T, heads * dv]: column slices of one product's result (one row
     stride); gates float32 [T, 2 heads]: pre-activations of the input gates, then of the forget gates;
     ``cap``: both are capped as cap * tanh(z / cap) (0: not); q is multiplied by ``qscale``.
-    state float32 [slots, heads, d * dv + d + 1].  Returns o float32 [T, heads * dv]."""
+    state float32 [slots, heads, d * dv + d + 1].  Returns o float32 [T, heads * dv].  ``q_lens`` (the
+    sequences' token counts of this step, host integers): if the longest has ``MLSTM_CHUNKED_FROM`` tokens or
+    more, the sequences are cut into chunks of ``MLSTM_CHUNK`` tokens that run side by side (three launches);
+    the results differ from the token-by-token walk by rounding only."""
     lib = build.load_library("mlstm")
     T = q.shape[0]
     assert q.shape == (T, heads * d) and k.shape == (T, heads * d) and v.shape == (T, heads * dv)
@@ -1419,10 +1427,20 @@ def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gates: torch.T
     assert bias_i.dtype is torch.float32 and bias_f.dtype is torch.float32 and bias_i.numel() == heads == bias_f.numel()
     assert state.dtype is torch.float32 and state.is_contiguous() and state.shape[1:] == (heads, mlstm_state_size(d, dv))
     out = torch.empty((T, heads * dv), dtype=torch.float32, device=q.device)
+    chunks, local, start = 0, None, None
+    if q_lens is not None and len(q_lens) == num_seqs and max(q_lens, default=0) >= MLSTM_CHUNKED_FROM:
+        chunks = sum(-(-int(n) // MLSTM_CHUNK) for n in q_lens)
+        per = mlstm_state_size(d, dv)
+        if chunks > 65535:
+            chunks = 0
+        else:
+            local = torch.empty((chunks, heads, per + 1), dtype=torch.float32, device=q.device)
+            start = torch.empty((chunks, heads, per), dtype=torch.float32, device=q.device)
     _check(lib.rllm_mlstm_scan(_ptr(q), _ptr(k), _ptr(v), c_int(q.stride(0)), c_int(dtype_code(q.dtype)), _ptr(gates),
                                _ptr(bias_i), _ptr(bias_f), c_float(cap), c_float(qscale), _ptr(state), _ptr(q_start),
                                _ptr(slots), _ptr(out), c_int(num_seqs), c_int(heads), c_int(d), c_int(dv),
-                               c_int(state.shape[0]), _ptr(err), _stream()), "mlstm_scan")
+                               c_int(state.shape[0]), c_int(chunks), _ptr(local), _ptr(start), _ptr(err), _stream()),
+           "mlstm_scan")
     return out
 
 

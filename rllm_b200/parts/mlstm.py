@@ -12,7 +12,8 @@ S [heads, d, dv], n [heads, d] and m [heads] are float32 per request, start at z
 carried from step to step in the request's state slot.  q, k, v and the output gate are one matrix
 product over the stacked weights; the two gates' pre-activations are a second one whose result stays
 float32 (they enter the recurrence); caps, logarithms, exponentials, the recurrence and the norm are
-float32 arithmetic in the kernels.
+float32 arithmetic in the kernels.  Portions of 129 tokens and more are scanned as chunks of 64 side by
+side (``ops.mlstm_scan``).
 
 params: hidden_size, num_heads, head_dim, v_dim, gate_cap (None or 0: no cap), eps,
 tensor_names (keys "q", "k", "v", "g", "o", "norm", "i", "i_bias", "f", "f_bias").
@@ -79,6 +80,6 @@ class MatrixLSTM(Mixer):
         gates = linear(x, self.w_gates, out_dtype=torch.float32)     # [T, 2 heads]: input gates | forget gates
         o = ops.mlstm_scan(a[:, :qk], a[:, qk:2 * qk], a[:, 2 * qk:2 * qk + vv], gates, self.b_i, self.b_f, self.cap,
                            float(self.d) ** -0.5, cache.state, ctx.q_start, ctx.state_slots, ctx.num_seqs,
-                           self.heads, self.d, self.dv, ctx.err)
+                           self.heads, self.d, self.dv, ctx.err, q_lens=ctx.q_lens_host)
         y = ops.head_gated_rmsnorm(o, a[:, 2 * qk + vv:], self.w_norm, self.eps, self.heads, x.dtype)
         return linear(y, self.w_o)

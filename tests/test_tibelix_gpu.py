@@ -98,6 +98,57 @@ def test_matrix_memory_in_steps_equals_the_plain_recurrence(dtype, H, d, dv, cap
         assert rel(torch.cat(got[s]), want[s]) <= (2e-5 if dtype == "float32" else 2e-2), s
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,d,dv,cap", [(3, 20, 36, 6.0), (2, 64, 128, 15.0)])
+def test_matrix_memory_in_chunks_side_by_side(dtype, H, d, dv, cap):
+    """Long portions take the chunked form (every chunk's end state from zero, the chunks' start states, then
+    every chunk from its start): three sequences of 400, 65 and 1 tokens in one call, the first one behind 37
+    tokens that were fed before; outputs and the states left behind equal the token-by-token walk's."""
+    from rllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(H + d + dv)
+    eps, lens, before = 1e-5, [437, 65, 1], [37, 0, 0]
+    data = []
+    for n in lens:
+        q, k = torch.randn(n, H, d, generator=g), torch.randn(n, H, d, generator=g)
+        v = torch.randn(n, H, dv, generator=g)
+        zi, zf = torch.randn(n, H, generator=g) * 3, torch.randn(n, H, generator=g) * 3 + 2
+        gate = torch.randn(n, H * dv, generator=g)
+        data.append([t.to(DT[dtype]).float() for t in (q, k, v)] + [zi, zf, gate.to(DT[dtype]).float()])
+    bi, bf = torch.randn(H, generator=g), torch.randn(H, generator=g)
+    norm_w = 1 + 0.1 * torch.randn(H * dv, generator=g)
+    want = [plain_memory(q, k, v, zi, zf, bi, bf, cap, eps, norm_w, gate) for q, k, v, zi, zf, gate in data]
+
+    def run(state, rows, q_lens):
+        """rows: (sequence, first token, count); returns the normalised outputs per row."""
+        parts = [torch.cat([data[s][j][a:a + n].reshape(n, -1) for s, a, n in rows]) for j in range(3)]
+        packed = torch.cat(parts + [torch.cat([data[s][5][a:a + n] for s, a, n in rows])], dim=1).to(DT[dtype]).cuda()
+        gates = torch.cat([torch.cat([data[s][3][a:a + n], data[s][4][a:a + n]], dim=1) for s, a, n in rows]).cuda()
+        q_start = [0]
+        for _, _, n in rows:
+            q_start.append(q_start[-1] + n)
+        err = err_word()
+        o = ops.mlstm_scan(packed[:, :H * d], packed[:, H * d:2 * H * d], packed[:, 2 * H * d:2 * H * d + H * dv], gates,
+                           bi.cuda(), bf.cuda(), cap, d ** -0.5, state, i32(q_start), i32([s for s, _, _ in rows]),
+                           len(rows), H, d, dv, err, q_lens=q_lens)
+        assert int(err.item()) == 0
+        return ops.head_gated_rmsnorm(o, packed[:, 2 * H * d + H * dv:], norm_w.cuda(), eps, H, DT[dtype]).float().cpu()
+
+    tol = 2e-5 if dtype == "float32" else 2e-2
+    states = []
+    for chunked in (True, False):
+        state = torch.zeros(3, H, ops.mlstm_state_size(d, dv), device="cuda")
+        run(state, [(0, 0, 37)], None)
+        rows = [(s, before[s], lens[s] - before[s]) for s in range(3)]
+        y = run(state, rows, [n for _, _, n in rows] if chunked else None)
+        at = 0
+        for s, a, n in rows:
+            assert rel(y[at:at + n], want[s][a:a + n]) <= tol, (chunked, s)
+            at += n
+        states.append(state.cpu())
+    scale = states[1].abs().amax(dim=2, keepdim=True)
+    assert float(((states[0] - states[1]).abs() / scale).max()) <= 1e-5
+
+
 # ---------------------------------------------------------------------------
 # attention: unit norms, temperature, distance bias, sink of score 0, gate per head
 # ---------------------------------------------------------------------------
@@ -167,6 +218,57 @@ def test_attention_with_unit_norms_temperature_distance_bias_and_sink(dtype, H, 
     first = out[0, :dv].double().cpu()
     whole = torch.sigmoid(gate[0, 0].to(DT[dtype]).double()) * v[0, 0].to(DT[dtype]).double()
     assert float(first.abs().max()) < 0.02 * float(whole.abs().max())
+
+
+@pytest.mark.parametrize("H,G,d,q_temp,page", [(4, 4, 64, None, 16), (8, 1, 32, (0.5, 16), 16), (8, 2, 128, (0.4, 50), 32),
+                                               (16, 4, 64, (0.5, 64), 64), (2, 1, 16, (0.3, 5), 16)])
+def test_tensor_core_attention_takes_the_distance_bias_the_sink_and_the_gate(H, G, d, q_temp, page):
+    """The bfloat16 kernels for keys and values of one size (prompt portions on mma.sync and, for heads of 64 and
+    128, on tcgen05; single tokens on the split-key decode kernel) against the plain rows: two sequences, the
+    second fed as a long portion behind cached tokens and as single tokens at several lengths; key 3 again
+    matches the last query of the last head from far back."""
+    from rllm_b200.kernels import ops
+    g = torch.Generator().manual_seed(H * d)
+    T, eps, scale = 330, 1e-5, 0.6 * (24.0 / d) ** 0.5
+    q, k = torch.randn(T, H, d, generator=g), torch.randn(T, G, d, generator=g)
+    v, gate = torch.randn(T, G, d, generator=g), torch.randn(T, H, generator=g) * 2
+    k[3, G - 1] = q[T - 1, H - 1] + 0.05 * torch.randn(d, generator=g)
+    bf = lambda t: t.bfloat16().float()
+    want = plain_attention_rows(bf(q), bf(k), bf(v), bf(gate), list(range(T)), scale, eps, q_temp)
+    width = H * d + 2 * G * d + H
+    width += (-width) % 8
+    rows = torch.zeros(T, width)
+    rows[:, :H * d + 2 * G * d + H] = torch.cat([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1), gate], dim=1)
+    pages = -(-T // page)
+    table = torch.randperm(pages + 3, generator=g)[:pages].to(torch.int32).view(1, pages).cuda()
+    kc = torch.zeros(pages + 3, G, page, d, dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    qkv, err = rows.bfloat16().cuda(), err_word()
+    pos, seq = i32(list(range(T))), i32([0] * T)
+    ops.head_norm_kv_write(qkv, pos, seq, None, None, eps, table, kc, vc, H, G, d, d, err, unit_norm=True, q_temp=q_temp)
+    slopes = torch.tensor(pt.distance_slopes(H), dtype=torch.float32, device="cuda")
+    sink = torch.zeros(H, device="cuda")
+    gcol = qkv[:, H * d + 2 * G * d: H * d + 2 * G * d + H]
+    opts = dict(sinks=sink, gate_per_head=True, slopes=slopes)
+    tol = 3e-2
+    # prompt portions: the whole sequence, and its last 200 tokens behind 130 cached ones
+    for first in (0, 130):
+        n = T - first
+        for kernel in (ops.attention_prefill_bf16, ops.attention_prefill_tcgen05):
+            if kernel is ops.attention_prefill_tcgen05 and not ops.attention_prefill_tcgen05_supported(H, G, d, page):
+                continue
+            out = torch.zeros(n, H * d, dtype=torch.bfloat16, device="cuda")
+            kernel(qkv[first:], width, out, kc, vc, table, i32([0, n]), i32([T]), 0, 1, n, H, G, d, 0, scale, err,
+                   gate=gcol[first:], **opts)
+            assert int(err.item()) == 0
+            assert rel(out, want[first:]) <= tol, (kernel.__name__, first)
+    # single tokens at lengths around chunk and page borders, and the last one (which reads key 3)
+    for n in (1, 2, page, page + 1, 128, 129, 257, T):
+        out = torch.zeros(1, H * d, dtype=torch.bfloat16, device="cuda")
+        ops.attention_decode_bf16(qkv[n - 1:n], width, out, kc, vc, table, i32([n]), 1, n, H, G, d, 0, scale, err,
+                                  gate=gcol[n - 1:n], **opts)
+        assert int(err.item()) == 0
+        assert float((out.double().cpu() - want[n - 1:n]).abs().max()) <= tol * float(want.abs().max()), n
 
 
 # ---------------------------------------------------------------------------
