@@ -13,10 +13,10 @@
 // Everything but the loads of q, k and v (which may be bfloat16) is float32 arithmetic;
 // the gates' pre-activations zi, zf arrive as float32.
 //
-//   mlstm_scan           one warp per (sequence, head, 32 value columns): it walks the
+//   mlstm_scan           one block per (sequence, head, 32 value columns): it walks the
 //                        sequence's tokens of this step in order with its slice of S in
-//                        shared memory and n in registers (every warp of a head carries n;
-//                        the first writes it back).  Long portions are cut into chunks of 64
+//                        registers (a warp 16 rows, a lane a column; n alike; every block of a
+//                        head carries n, the first writes it back).  Long portions are cut into chunks of 64
 //                        tokens that run side by side: every chunk's end state from zero, then
 //                        the states at the chunks' starts chunk after chunk (an elementwise
 //                        pass), then every chunk's tokens from its start state.  Either way a
@@ -40,22 +40,44 @@ __device__ __forceinline__ float ml_logsigmoid(float x) { return fminf(x, 0.f) -
 // Units of MODE 1 and 2 are numbered sequence by sequence; a block finds its sequence by walking q_start.
 #define ML_CHUNK 64
 
-template <typename T, int MODE>
-__global__ void __launch_bounds__(32)
-mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* gates, const float* bias_i,
-                  const float* bias_f, float cap, float qscale, float* state, const int* q_start, const int* slots,
-                  float* out, int num_seqs, int heads, int d, int dv, int num_slots, float* local, float* start,
-                  int* err) {
+#define ML_R 16                 // rows of S a thread keeps in registers
+
+// the gates' pre-activations become the log gates, in place: gates[t][h] <- a, gates[t][heads + h] <- b
+__global__ void __launch_bounds__(256)
+mlstm_gates_kernel(float* gates, const float* bias_i, const float* bias_f, float cap, long long n, int heads) {
   pdl_wait();
   pdl_launch();
-  extern __shared__ float sm[];          // S slice [d][32], then k [d], then q [d]
-  float* S = sm;
-  float* ks = sm + (size_t)d * 32;
-  float* qs = ks + d;
-  const int lane = threadIdx.x;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n) return;
+  const long long t = idx / heads;
+  const int h = (int)(idx - t * heads);
+  float* g = gates + t * 2 * heads;
+  g[h] = ml_soft_cap(g[h] + (bias_i ? bias_i[h] : 0.f), cap);
+  g[heads + h] = ml_logsigmoid(ml_soft_cap(g[heads + h] + (bias_f ? bias_f[h] : 0.f), cap));
+}
+
+// A block: (32 value columns, head, unit); warp w keeps rows w * ML_R .. of its columns of S in registers (a
+// lane a column) and lanes 0 .. ML_R - 1 of it the same rows of n.  A token: the weighted keys and the scaled
+// queries are staged in shared memory (two buffers, so one barrier a token serves), every thread updates its
+// rows and adds up its part of S^T q; the warps' parts (and those of n . q) meet in shared memory, and the first
+// warp finishes the token before last while the others work on.  The next token's values are fetched ahead.
+template <typename T, int MODE>
+__global__ void __launch_bounds__(512)
+mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* gates, float qscale, float* state,
+                  const int* q_start, const int* slots, float* out, int num_seqs, int heads, int d, int dv,
+                  int num_slots, float* local, float* start, int* err) {
+  pdl_wait();
+  pdl_launch();
+  extern __shared__ __align__(16) float sm[];
+  const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, W = blockDim.x >> 5;
+  const int dpad = W * ML_R;
+  float* ksb = sm;                       // [2][dpad]: exp(a - m) k
+  float* qsb = sm + 2 * dpad;            // [2][dpad]: q * qscale
+  float* part = sm + 4 * dpad;           // [2][W][33]: the warps' parts of S^T q for 32 columns, and of n . q
   const int j = blockIdx.x * 32 + lane;  // value column
   const int h = blockIdx.y;
-  int s = blockIdx.z, t0, t1, unit = blockIdx.z;
+  int s = blockIdx.z, t0, t1;
+  const int unit = blockIdx.z;
   bool last_chunk = true;
   if (MODE == 0) {
     t0 = q_start[s];
@@ -74,9 +96,10 @@ mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* g
     last_chunk = t1 == q_start[s + 1];
     if (MODE == 1 && last_chunk) return;             // nobody reads the end state of a sequence's last chunk
   }
+  if (t1 <= t0) return;
   const int slot = slots[s];
   if (slot < 0 || slot >= num_slots) {
-    if (lane == 0) atomicOr(err, 8);
+    if (tid == 0) atomicOr(err, 8);
     return;
   }
   const size_t per_head = (size_t)d * dv + d + 1;
@@ -85,90 +108,93 @@ mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* g
   // sequence's last chunk, which may run at the same time)
   const float* from = MODE == 2 ? start + ((size_t)unit * heads + h) * per_head : st;
   const bool live = j < dv;
-  float n[ML_MAX_D / 32];
-  float m;
-  if (MODE == 1) {
-    for (int i = 0; i < d; ++i) S[i * 32 + lane] = 0.f;
+  const int i0 = w * ML_R;
+  const int ni = i0 + lane;              // the row of n this lane keeps (lanes below ML_R)
+  float S[ML_R];
+  float nreg = 0.f, m = -INFINITY, bsum = 0.f;
 #pragma unroll
-    for (int r = 0; r < ML_MAX_D / 32; ++r) n[r] = 0.f;
-    m = -INFINITY;
-  } else {
-    for (int i = 0; i < d; ++i) S[i * 32 + lane] = live ? from[(size_t)i * dv + j] : 0.f;
-#pragma unroll
-    for (int r = 0; r < ML_MAX_D / 32; ++r) {
-      const int i = lane + 32 * r;
-      n[r] = i < d ? from[(size_t)d * dv + i] : 0.f;
-    }
+  for (int r = 0; r < ML_R; ++r) S[r] = (MODE != 1 && live && i0 + r < d) ? from[(size_t)(i0 + r) * dv + j] : 0.f;
+  if (MODE != 1) {
+    if (lane < ML_R && ni < d) nreg = from[(size_t)d * dv + ni];
     m = from[(size_t)d * dv + d];
   }
-  const float bi = bias_i ? bias_i[h] : 0.f, bf = bias_f ? bias_f[h] : 0.f;
-  float bsum = 0.f;
-  // the next token's values are fetched while this token's are worked on
-  float nk[ML_MAX_D / 32], nq[ML_MAX_D / 32], nv = 0.f, nzi = 0.f, nzf = 0.f;
+  float pk = 0.f, pq = 0.f, pv = 0.f, pa = 0.f, pb = 0.f;
   auto fetch = [&](int t) {
-    const T* qr = q + (size_t)t * stride + (size_t)h * d;
-    const T* kr = k + (size_t)t * stride + (size_t)h * d;
-#pragma unroll
-    for (int r = 0; r < ML_MAX_D / 32; ++r) {
-      const int i = lane + 32 * r;
-      if (i < d) { nk[r] = to_f32(kr[i]); if (MODE != 1) nq[r] = to_f32(qr[i]); }
+    if (tid < d) {
+      pk = to_f32(k[(size_t)t * stride + (size_t)h * d + tid]);
+      if (MODE != 1) pq = to_f32(q[(size_t)t * stride + (size_t)h * d + tid]);
     }
-    nv = live ? to_f32(v[(size_t)t * stride + (size_t)h * dv + j]) : 0.f;
-    nzi = gates[(size_t)t * 2 * heads + h];
-    nzf = gates[(size_t)t * 2 * heads + heads + h];
+    pv = live ? to_f32(v[(size_t)t * stride + (size_t)h * dv + j]) : 0.f;
+    pa = gates[(size_t)t * 2 * heads + h];
+    pb = gates[(size_t)t * 2 * heads + heads + h];
   };
-  if (t0 < t1) fetch(t0);
-  for (int t = t0; t < t1; ++t) {
-    const float a = ml_soft_cap(nzi + bi, cap);
-    const float b = ml_logsigmoid(ml_soft_cap(nzf + bf, cap));
-    const float m_new = fmaxf(b + m, a);
-    const float keep = expf(b + m - m_new), take = expf(a - m_new);
-    m = m_new;
-    bsum += b;
-    __syncwarp();
-#pragma unroll
-    for (int r = 0; r < ML_MAX_D / 32; ++r) {
-      const int i = lane + 32 * r;
-      if (i < d) { ks[i] = take * nk[r]; if (MODE != 1) qs[i] = nq[r] * qscale; }
+  auto finish = [&](int t, int buf, float mt) {       // the first warp: the parts of token t become its output
+    float num = 0.f, dot = 0.f;
+    for (int x = 0; x < W; ++x) {
+      num += part[(buf * W + x) * 33 + lane];
+      dot += part[(buf * W + x) * 33 + 32];
     }
-    const float vj = nv;
-    __syncwarp();
-    if (t + 1 < t1) fetch(t + 1);
-    float part = 0.f;
-#pragma unroll
-    for (int r = 0; r < ML_MAX_D / 32; ++r) {
-      const int i = lane + 32 * r;
-      if (i < d) { n[r] = fmaf(keep, n[r], ks[i]); if (MODE != 1) part = fmaf(n[r], qs[i], part); }
-    }
-    if (MODE == 1) {
-#pragma unroll 4
-      for (int i = 0; i < d; ++i) S[i * 32 + lane] = fmaf(keep, S[i * 32 + lane], ks[i] * vj);
-      continue;
-    }
-    const float dot = warp_sum(part);
-    float num = 0.f;
-#pragma unroll 4
-    for (int i = 0; i < d; ++i) {
-      const float sij = fmaf(keep, S[i * 32 + lane], ks[i] * vj);
-      S[i * 32 + lane] = sij;
-      num = fmaf(sij, qs[i], num);
-    }
-    const float den = fmaxf(fabsf(dot), expf(-m)) + 1e-6f;
+    const float den = fmaxf(fabsf(dot), expf(-mt)) + 1e-6f;
     if (live) out[(size_t)t * heads * dv + (size_t)h * dv + j] = num / den;
+  };
+  fetch(t0);
+  for (int t = t0; t < t1; ++t) {
+    const int buf = (t - t0) & 1;
+    const float m_new = fmaxf(pb + m, pa);
+    const float keep = expf(pb + m - m_new), take = expf(pa - m_new);
+    bsum += pb;
+    if (tid < dpad) {
+      ksb[buf * dpad + tid] = tid < d ? take * pk : 0.f;
+      if (MODE != 1) qsb[buf * dpad + tid] = tid < d ? pq * qscale : 0.f;
+    }
+    const float vj = pv;
+    if (t + 1 < t1) fetch(t + 1);
+    __syncthreads();
+    if (MODE != 1 && w == 0 && t > t0) finish(t - 1, buf ^ 1, m);
+    m = m_new;
+    const float4* k4 = (const float4*)(ksb + buf * dpad + i0);
+    const float4* q4 = (const float4*)(qsb + buf * dpad + i0);
+    float num0 = 0.f, num1 = 0.f;
+#pragma unroll
+    for (int r4 = 0; r4 < ML_R / 4; ++r4) {
+      const float4 kk = k4[r4];
+      S[4 * r4 + 0] = fmaf(keep, S[4 * r4 + 0], kk.x * vj);
+      S[4 * r4 + 1] = fmaf(keep, S[4 * r4 + 1], kk.y * vj);
+      S[4 * r4 + 2] = fmaf(keep, S[4 * r4 + 2], kk.z * vj);
+      S[4 * r4 + 3] = fmaf(keep, S[4 * r4 + 3], kk.w * vj);
+      if (MODE != 1) {
+        const float4 qq = q4[r4];
+        num0 = fmaf(S[4 * r4 + 0], qq.x, num0);
+        num1 = fmaf(S[4 * r4 + 1], qq.y, num1);
+        num0 = fmaf(S[4 * r4 + 2], qq.z, num0);
+        num1 = fmaf(S[4 * r4 + 3], qq.w, num1);
+      }
+    }
+    float pd = 0.f;
+    if (lane < ML_R) {
+      nreg = fmaf(keep, nreg, ksb[buf * dpad + ni]);
+      if (MODE != 1) pd = nreg * qsb[buf * dpad + ni];
+    }
+    if (MODE != 1) {
+      pd = warp_sum(pd);
+      part[(buf * W + w) * 33 + lane] = num0 + num1;
+      if (lane == 0) part[(buf * W + w) * 33 + 32] = pd;
+    }
   }
-  if (t1 <= t0) return;
+  if (MODE != 1) {
+    __syncthreads();
+    if (w == 0) finish(t1 - 1, (t1 - 1 - t0) & 1, m);
+  }
   float* to = nullptr;
   if (MODE == 0 || (MODE == 2 && last_chunk)) to = st;
   if (MODE == 1) to = local + ((size_t)unit * heads + h) * (per_head + 1);
   if (to == nullptr) return;
-  if (live) for (int i = 0; i < d; ++i) to[(size_t)i * dv + j] = S[i * 32 + lane];
-  if (blockIdx.x == 0) {
 #pragma unroll
-    for (int r = 0; r < ML_MAX_D / 32; ++r) {
-      const int i = lane + 32 * r;
-      if (i < d) to[(size_t)d * dv + i] = n[r];
-    }
-    if (lane == 0) {
+  for (int r = 0; r < ML_R; ++r)
+    if (live && i0 + r < d) to[(size_t)(i0 + r) * dv + j] = S[r];
+  if (blockIdx.x == 0) {
+    if (lane < ML_R && ni < d) to[(size_t)d * dv + ni] = nreg;
+    if (tid == 0) {
       to[(size_t)d * dv + d] = m;
       if (MODE == 1) to[(size_t)d * dv + d + 1] = bsum;
     }
@@ -210,28 +236,30 @@ mlstm_chunk_starts_kernel(const float* state, const int* q_start, const int* slo
 
 // q, k: rows of heads * d; v: rows of heads * dv; all three with the row stride `stride` (views into one
 // product's result).  gates float32 [T, 2 heads]: the input gates' pre-activations, then the forget gates'.
+// They are turned into the log gates in place by a first launch.
 // state float32 [slots, heads, d * dv + d + 1]; out float32 [T, heads * dv].
 // chunks > 0 (the number of chunks of ML_CHUNK tokens over all sequences, each sequence cut from its first token
 // of this step) with workspaces local [chunks, heads, d * dv + d + 2] and start [chunks, heads, d * dv + d + 1]:
 // three launches that work on all chunks side by side; chunks == 0: one warp walks a sequence's tokens.
-RLLM_EXPORT int rllm_mlstm_scan(const void* q, const void* k, const void* v, int stride, int dtype, const float* gates,
+RLLM_EXPORT int rllm_mlstm_scan(const void* q, const void* k, const void* v, int stride, int dtype, float* gates,
                                 const float* bias_i, const float* bias_f, float cap, float qscale, float* state,
-                                const int* q_start, const int* slots, float* out, int num_seqs, int heads, int d,
-                                int dv, int num_slots, int chunks, float* local, float* start, int* err,
-                                cudaStream_t stream) {
-  if (num_seqs <= 0) return 0;
+                                const int* q_start, const int* slots, float* out, int num_tokens, int num_seqs,
+                                int heads, int d, int dv, int num_slots, int chunks, float* local, float* start,
+                                int* err, cudaStream_t stream) {
+  if (num_seqs <= 0 || num_tokens <= 0) return 0;
   if (heads <= 0 || d <= 0 || dv <= 0 || num_slots <= 0 || !(cap >= 0.f) || chunks < 0) return RLLM_E_BADARG;
   if (chunks > 0 && (!local || !start)) return RLLM_E_BADARG;
   if (d > ML_MAX_D || heads > 65535 || num_seqs > 65535 || chunks > 65535) return RLLM_E_UNSUPPORTED;
-  const size_t smem = ((size_t)d * 32 + 2 * (size_t)d) * sizeof(float);
+  const int W = (d + ML_R - 1) / ML_R;
+  const size_t smem = ((size_t)4 * W * ML_R + 2 * (size_t)W * 33) * sizeof(float);
+  const long long ng = (long long)num_tokens * heads;
+  rllm_launch_pdl(mlstm_gates_kernel, dim3((unsigned)((ng + 255) / 256)), dim3(256), (size_t)0, stream, gates, bias_i,
+                  bias_f, cap, ng, heads);
+  RLLM_LAUNCH_CHECK();
 #define ML_GO(T_, MODE_, UNITS_)                                                                               \
-  do {                                                                                                         \
-    if (smem > 48 * 1024)                                                                                      \
-      cudaFuncSetAttribute(mlstm_scan_kernel<T_, MODE_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    rllm_launch_pdl(mlstm_scan_kernel<T_, MODE_>, dim3((dv + 31) / 32, heads, UNITS_), dim3(32), smem, stream,  \
-                    (const T_*)q, (const T_*)k, (const T_*)v, stride, gates, bias_i, bias_f, cap, qscale, state, \
-                    q_start, slots, out, num_seqs, heads, d, dv, num_slots, local, start, err);                \
-  } while (0)
+  rllm_launch_pdl(mlstm_scan_kernel<T_, MODE_>, dim3((dv + 31) / 32, heads, UNITS_), dim3(32 * W), smem, stream, \
+                  (const T_*)q, (const T_*)k, (const T_*)v, stride, (const float*)gates, qscale, state, q_start,  \
+                  slots, out, num_seqs, heads, d, dv, num_slots, local, start, err)
   if (chunks == 0) {
     RLLM_DISPATCH_DTYPE(dtype, TT, ML_GO(TT, 0, num_seqs));
   } else {

@@ -1412,7 +1412,8 @@ def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gates: torch.T
                q_lens=None) -> torch.Tensor:
     """The mLSTM recurrence over this step's tokens of every sequence, in order, from and into the sequences'
     state slots.  q, k [T, heads * d] and v [T, heads * dv]: column slices of one product's result (one row
-    stride); gates float32 [T, 2 heads]: pre-activations of the input gates, then of the forget gates;
+    stride); gates float32 [T, 2 heads]: pre-activations of the input gates, then of the forget gates (the
+    call turns them into the log gates in place);
     ``cap``: both are capped as cap * tanh(z / cap) (0: not); q is multiplied by ``qscale``.
     state float32 [slots, heads, d * dv + d + 1].  Returns o float32 [T, heads * dv].  ``q_lens`` (the
     sequences' token counts of this step, host integers): if the longest has ``MLSTM_CHUNKED_FROM`` tokens or
@@ -1438,7 +1439,7 @@ def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gates: torch.T
             start = torch.empty((chunks, heads, per), dtype=torch.float32, device=q.device)
     _check(lib.rllm_mlstm_scan(_ptr(q), _ptr(k), _ptr(v), c_int(q.stride(0)), c_int(dtype_code(q.dtype)), _ptr(gates),
                                _ptr(bias_i), _ptr(bias_f), c_float(cap), c_float(qscale), _ptr(state), _ptr(q_start),
-                               _ptr(slots), _ptr(out), c_int(num_seqs), c_int(heads), c_int(d), c_int(dv),
+                               _ptr(slots), _ptr(out), c_int(T), c_int(num_seqs), c_int(heads), c_int(d), c_int(dv),
                                c_int(state.shape[0]), c_int(chunks), _ptr(local), _ptr(start), _ptr(err), _stream()),
            "mlstm_scan")
     return out
