@@ -13,9 +13,9 @@
 // Everything but the loads of q, k and v (which may be bfloat16) is float32 arithmetic;
 // the gates' pre-activations zi, zf arrive as float32.
 //
-//   mlstm_scan           one block per (sequence, head, 32 value columns): it walks the
+//   mlstm_scan           one block per (sequence, head, 64 value columns): it walks the
 //                        sequence's tokens of this step in order with its slice of S in
-//                        registers (a warp 16 rows, a lane a column; n alike; every block of a
+//                        registers (a warp 16 rows, a lane two columns; n alike; every block of a
 //                        head carries n, the first writes it back).  Long portions are cut into chunks of 64
 //                        tokens that run side by side: every chunk's end state from zero, then
 //                        the states at the chunks' starts chunk after chunk (an elementwise
@@ -56,11 +56,18 @@ mlstm_gates_kernel(float* gates, const float* bias_i, const float* bias_f, float
   g[heads + h] = ml_logsigmoid(ml_soft_cap(g[heads + h] + (bias_f ? bias_f[h] : 0.f), cap));
 }
 
-// A block: (32 value columns, head, unit); warp w keeps rows w * ML_R .. of its columns of S in registers (a
-// lane a column) and lanes 0 .. ML_R - 1 of it the same rows of n.  A token: the weighted keys and the scaled
-// queries are staged in shared memory (two buffers, so one barrier a token serves), every thread updates its
-// rows and adds up its part of S^T q; the warps' parts (and those of n . q) meet in shared memory, and the first
-// warp finishes the token before last while the others work on.  The next token's values are fetched ahead.
+// A block: (64 value columns, head, unit); warp w keeps rows w * ML_R .. of its columns of S in registers (a
+// lane two columns, 32 apart) and lanes 0 .. ML_R - 1 of it the same rows of n.  Tokens go in segments of
+// ML_CHUNK: first the segment's factors exp(b + m' - m), exp(a - m) and maxima m are made once for all threads
+// (the gates fetched side by side, the chain over m walked by one thread).  Then four tokens at a time: their
+// weighted keys and scaled queries are staged in shared memory (two buffers, so one barrier a group serves),
+// every thread updates its rows token after token and adds up its parts of S^T q; the warps' parts (and those of
+// n . q) meet in shared memory, and the first warp finishes the group before last while the others work on.  The
+// next group's values are fetched ahead.
+#define ML_COLS 64
+#define ML_G 4                  // tokens between two barriers
+#define ML_PART (ML_COLS + 1)
+
 template <typename T, int MODE>
 __global__ void __launch_bounds__(512)
 mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* gates, float qscale, float* state,
@@ -69,12 +76,13 @@ mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* g
   pdl_wait();
   pdl_launch();
   extern __shared__ __align__(16) float sm[];
+  __shared__ float g_keep[ML_CHUNK], g_take[ML_CHUNK], g_m[ML_CHUNK];
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, W = blockDim.x >> 5;
   const int dpad = W * ML_R;
-  float* ksb = sm;                       // [2][dpad]: exp(a - m) k
-  float* qsb = sm + 2 * dpad;            // [2][dpad]: q * qscale
-  float* part = sm + 4 * dpad;           // [2][W][33]: the warps' parts of S^T q for 32 columns, and of n . q
-  const int j = blockIdx.x * 32 + lane;  // value column
+  float* ksb = sm;                       // [2][ML_G][dpad]: exp(a - m) k
+  float* qsb = sm + 2 * ML_G * dpad;     // [2][ML_G][dpad]: q * qscale
+  float* part = sm + 4 * ML_G * dpad;    // [2][ML_G][W][65]: the warps' parts of S^T q for 64 columns, and of n . q
+  const int j0 = blockIdx.x * ML_COLS + lane, j1 = j0 + 32;      // this lane's value columns
   const int h = blockIdx.y;
   int s = blockIdx.z, t0, t1;
   const int unit = blockIdx.z;
@@ -107,91 +115,135 @@ mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* g
   // (MODE 2 reads every chunk's start state, the first one's too, from `start`: the slot is written by the
   // sequence's last chunk, which may run at the same time)
   const float* from = MODE == 2 ? start + ((size_t)unit * heads + h) * per_head : st;
-  const bool live = j < dv;
+  const bool live0 = j0 < dv, live1 = j1 < dv;
   const int i0 = w * ML_R;
   const int ni = i0 + lane;              // the row of n this lane keeps (lanes below ML_R)
-  float S[ML_R];
-  float nreg = 0.f, m = -INFINITY, bsum = 0.f;
+  float S0[ML_R], S1[ML_R];
+  float nreg = 0.f, m = -INFINITY, bsum = 0.f;       // m, bsum: the first thread's
 #pragma unroll
-  for (int r = 0; r < ML_R; ++r) S[r] = (MODE != 1 && live && i0 + r < d) ? from[(size_t)(i0 + r) * dv + j] : 0.f;
+  for (int r = 0; r < ML_R; ++r) {
+    S0[r] = (MODE != 1 && live0 && i0 + r < d) ? from[(size_t)(i0 + r) * dv + j0] : 0.f;
+    S1[r] = (MODE != 1 && live1 && i0 + r < d) ? from[(size_t)(i0 + r) * dv + j1] : 0.f;
+  }
   if (MODE != 1) {
     if (lane < ML_R && ni < d) nreg = from[(size_t)d * dv + ni];
     m = from[(size_t)d * dv + d];
   }
-  float pk = 0.f, pq = 0.f, pv = 0.f, pa = 0.f, pb = 0.f;
-  auto fetch = [&](int t) {
-    if (tid < d) {
-      pk = to_f32(k[(size_t)t * stride + (size_t)h * d + tid]);
-      if (MODE != 1) pq = to_f32(q[(size_t)t * stride + (size_t)h * d + tid]);
-    }
-    pv = live ? to_f32(v[(size_t)t * stride + (size_t)h * dv + j]) : 0.f;
-    pa = gates[(size_t)t * 2 * heads + h];
-    pb = gates[(size_t)t * 2 * heads + heads + h];
-  };
-  auto finish = [&](int t, int buf, float mt) {       // the first warp: the parts of token t become its output
-    float num = 0.f, dot = 0.f;
-    for (int x = 0; x < W; ++x) {
-      num += part[(buf * W + x) * 33 + lane];
-      dot += part[(buf * W + x) * 33 + 32];
-    }
-    const float den = fmaxf(fabsf(dot), expf(-mt)) + 1e-6f;
-    if (live) out[(size_t)t * heads * dv + (size_t)h * dv + j] = num / den;
-  };
-  fetch(t0);
-  for (int t = t0; t < t1; ++t) {
-    const int buf = (t - t0) & 1;
-    const float m_new = fmaxf(pb + m, pa);
-    const float keep = expf(pb + m - m_new), take = expf(pa - m_new);
-    bsum += pb;
-    if (tid < dpad) {
-      ksb[buf * dpad + tid] = tid < d ? take * pk : 0.f;
-      if (MODE != 1) qsb[buf * dpad + tid] = tid < d ? pq * qscale : 0.f;
-    }
-    const float vj = pv;
-    if (t + 1 < t1) fetch(t + 1);
-    __syncthreads();
-    if (MODE != 1 && w == 0 && t > t0) finish(t - 1, buf ^ 1, m);
-    m = m_new;
-    const float4* k4 = (const float4*)(ksb + buf * dpad + i0);
-    const float4* q4 = (const float4*)(qsb + buf * dpad + i0);
-    float num0 = 0.f, num1 = 0.f;
+  // Tokens go through in groups of ML_G between two barriers.  Thread tid < dpad stages element tid of the
+  // group's keys, thread dpad + e element e of its queries (the block has exactly 2 dpad threads).
+  const bool stage_q = tid >= dpad;
+  const int se = stage_q ? tid - dpad : tid;
+  float pst[ML_G], pv0[ML_G], pv1[ML_G];
+  auto fetch = [&](int t, int end) {                   // tokens t .. t + ML_G - 1 (those before `end`)
 #pragma unroll
-    for (int r4 = 0; r4 < ML_R / 4; ++r4) {
-      const float4 kk = k4[r4];
-      S[4 * r4 + 0] = fmaf(keep, S[4 * r4 + 0], kk.x * vj);
-      S[4 * r4 + 1] = fmaf(keep, S[4 * r4 + 1], kk.y * vj);
-      S[4 * r4 + 2] = fmaf(keep, S[4 * r4 + 2], kk.z * vj);
-      S[4 * r4 + 3] = fmaf(keep, S[4 * r4 + 3], kk.w * vj);
-      if (MODE != 1) {
-        const float4 qq = q4[r4];
-        num0 = fmaf(S[4 * r4 + 0], qq.x, num0);
-        num1 = fmaf(S[4 * r4 + 1], qq.y, num1);
-        num0 = fmaf(S[4 * r4 + 2], qq.z, num0);
-        num1 = fmaf(S[4 * r4 + 3], qq.w, num1);
+    for (int x = 0; x < ML_G; ++x) {
+      const bool in = t + x < end;
+      pst[x] = 0.f;
+      if (in && se < d && !(MODE == 1 && stage_q))
+        pst[x] = to_f32((stage_q ? q : k)[(size_t)(t + x) * stride + (size_t)h * d + se]);
+      pv0[x] = (in && live0) ? to_f32(v[(size_t)(t + x) * stride + (size_t)h * dv + j0]) : 0.f;
+      pv1[x] = (in && live1) ? to_f32(v[(size_t)(t + x) * stride + (size_t)h * dv + j1]) : 0.f;
+    }
+  };
+  auto finish = [&](int t, int end, int buf, int g0) { // the first warp: the parts of tokens t .. become outputs
+    for (int x = 0; x < ML_G && t + x < end; ++x) {
+      float num0 = 0.f, num1 = 0.f, dot = 0.f;
+      const float* pp = part + (size_t)((buf * ML_G + x) * W) * ML_PART;
+      for (int y = 0; y < W; ++y) {
+        num0 += pp[y * ML_PART + lane];
+        num1 += pp[y * ML_PART + 32 + lane];
+        dot += pp[y * ML_PART + ML_COLS];
+      }
+      const float inv = 1.0f / (fmaxf(fabsf(dot), expf(-g_m[g0 + x])) + 1e-6f);
+      if (live0) out[(size_t)(t + x) * heads * dv + (size_t)h * dv + j0] = num0 * inv;
+      if (live1) out[(size_t)(t + x) * heads * dv + (size_t)h * dv + j1] = num1 * inv;
+    }
+  };
+  for (int seg = t0; seg < t1; seg += ML_CHUNK) {
+    const int seg_end = min(seg + ML_CHUNK, t1);
+    fetch(seg, seg_end);
+    // the segment's gates side by side, then the chain over the maximum by one thread; places behind the
+    // segment's end get the factors that leave the state as it is
+    for (int x = tid; x < seg_end - seg; x += blockDim.x) {
+      g_keep[x] = gates[(size_t)(seg + x) * 2 * heads + heads + h];         // b
+      g_take[x] = gates[(size_t)(seg + x) * 2 * heads + h];                 // a
+    }
+    __syncthreads();
+    if (tid == 0) {
+      const int padded = (seg_end - seg + ML_G - 1) / ML_G * ML_G;         // the last group is filled up
+      for (int x = 0; x < padded; ++x) {
+        if (x >= seg_end - seg) { g_keep[x] = 1.f; g_take[x] = 0.f; g_m[x] = m; continue; }
+        const float b = g_keep[x], a = g_take[x];
+        const float m_new = fmaxf(b + m, a);
+        g_keep[x] = expf(b + m - m_new);
+        g_take[x] = expf(a - m_new);
+        g_m[x] = m_new;
+        m = m_new;
+        bsum += b;
       }
     }
-    float pd = 0.f;
-    if (lane < ML_R) {
-      nreg = fmaf(keep, nreg, ksb[buf * dpad + ni]);
-      if (MODE != 1) pd = nreg * qsb[buf * dpad + ni];
-    }
-    if (MODE != 1) {
-      pd = warp_sum(pd);
-      part[(buf * W + w) * 33 + lane] = num0 + num1;
-      if (lane == 0) part[(buf * W + w) * 33 + 32] = pd;
-    }
-  }
-  if (MODE != 1) {
     __syncthreads();
-    if (w == 0) finish(t1 - 1, (t1 - 1 - t0) & 1, m);
+    int grp = 0;
+    for (int t = seg; t < seg_end; t += ML_G, ++grp) {
+      const int buf = grp & 1, g0 = grp * ML_G;
+      float v0[ML_G], v1[ML_G];
+#pragma unroll
+      for (int x = 0; x < ML_G; ++x) {
+        float* dst = (stage_q ? qsb : ksb) + (size_t)(buf * ML_G + x) * dpad + se;
+        if (!(MODE == 1 && stage_q)) *dst = pst[x] * (stage_q ? qscale : g_take[g0 + x]);
+        v0[x] = pv0[x];
+        v1[x] = pv1[x];
+      }
+      if (t + ML_G < seg_end) fetch(t + ML_G, seg_end);
+      __syncthreads();
+      if (MODE != 1 && w == 0 && grp > 0) finish(t - ML_G, seg_end, buf ^ 1, g0 - ML_G);
+#pragma unroll
+      for (int x = 0; x < ML_G; ++x) {
+        const float keep = g_keep[g0 + x];
+        const float4* k4 = (const float4*)(ksb + (size_t)(buf * ML_G + x) * dpad + i0);
+        const float4* q4 = (const float4*)(qsb + (size_t)(buf * ML_G + x) * dpad + i0);
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int r4 = 0; r4 < ML_R / 4; ++r4) {
+          const float4 kk = k4[r4];
+          S0[4 * r4 + 0] = fmaf(keep, S0[4 * r4 + 0], kk.x * v0[x]);  S1[4 * r4 + 0] = fmaf(keep, S1[4 * r4 + 0], kk.x * v1[x]);
+          S0[4 * r4 + 1] = fmaf(keep, S0[4 * r4 + 1], kk.y * v0[x]);  S1[4 * r4 + 1] = fmaf(keep, S1[4 * r4 + 1], kk.y * v1[x]);
+          S0[4 * r4 + 2] = fmaf(keep, S0[4 * r4 + 2], kk.z * v0[x]);  S1[4 * r4 + 2] = fmaf(keep, S1[4 * r4 + 2], kk.z * v1[x]);
+          S0[4 * r4 + 3] = fmaf(keep, S0[4 * r4 + 3], kk.w * v0[x]);  S1[4 * r4 + 3] = fmaf(keep, S1[4 * r4 + 3], kk.w * v1[x]);
+          if (MODE != 1) {
+            const float4 qq = q4[r4];
+            a0 = fmaf(S0[4 * r4 + 0], qq.x, a0);  a1 = fmaf(S1[4 * r4 + 0], qq.x, a1);
+            a0 = fmaf(S0[4 * r4 + 1], qq.y, a0);  a1 = fmaf(S1[4 * r4 + 1], qq.y, a1);
+            a0 = fmaf(S0[4 * r4 + 2], qq.z, a0);  a1 = fmaf(S1[4 * r4 + 2], qq.z, a1);
+            a0 = fmaf(S0[4 * r4 + 3], qq.w, a0);  a1 = fmaf(S1[4 * r4 + 3], qq.w, a1);
+          }
+        }
+        float pd = 0.f;
+        if (lane < ML_R) {
+          nreg = fmaf(keep, nreg, ksb[(size_t)(buf * ML_G + x) * dpad + ni]);
+          if (MODE != 1) pd = nreg * qsb[(size_t)(buf * ML_G + x) * dpad + ni];
+        }
+        if (MODE != 1) {
+          pd = warp_sum(pd);
+          float* pp = part + (size_t)((buf * ML_G + x) * W + w) * ML_PART;
+          pp[lane] = a0;
+          pp[32 + lane] = a1;
+          if (lane == 0) pp[ML_COLS] = pd;
+        }
+      }
+    }
+    __syncthreads();          // the segment's last parts are in; and everybody is through with its factors
+    if (MODE != 1 && w == 0) finish(seg + (grp - 1) * ML_G, seg_end, (grp - 1) & 1, (grp - 1) * ML_G);
   }
   float* to = nullptr;
   if (MODE == 0 || (MODE == 2 && last_chunk)) to = st;
   if (MODE == 1) to = local + ((size_t)unit * heads + h) * (per_head + 1);
   if (to == nullptr) return;
 #pragma unroll
-  for (int r = 0; r < ML_R; ++r)
-    if (live && i0 + r < d) to[(size_t)(i0 + r) * dv + j] = S[r];
+  for (int r = 0; r < ML_R; ++r) {
+    if (live0 && i0 + r < d) to[(size_t)(i0 + r) * dv + j0] = S0[r];
+    if (live1 && i0 + r < d) to[(size_t)(i0 + r) * dv + j1] = S1[r];
+  }
   if (blockIdx.x == 0) {
     if (lane < ML_R && ni < d) to[(size_t)d * dv + ni] = nreg;
     if (tid == 0) {
@@ -251,13 +303,15 @@ RLLM_EXPORT int rllm_mlstm_scan(const void* q, const void* k, const void* v, int
   if (chunks > 0 && (!local || !start)) return RLLM_E_BADARG;
   if (d > ML_MAX_D || heads > 65535 || num_seqs > 65535 || chunks > 65535) return RLLM_E_UNSUPPORTED;
   const int W = (d + ML_R - 1) / ML_R;
-  const size_t smem = ((size_t)4 * W * ML_R + 2 * (size_t)W * 33) * sizeof(float);
+  const size_t smem = ((size_t)4 * ML_G * W * ML_R + 2 * (size_t)ML_G * W * ML_PART) * sizeof(float);
   const long long ng = (long long)num_tokens * heads;
   rllm_launch_pdl(mlstm_gates_kernel, dim3((unsigned)((ng + 255) / 256)), dim3(256), (size_t)0, stream, gates, bias_i,
                   bias_f, cap, ng, heads);
   RLLM_LAUNCH_CHECK();
 #define ML_GO(T_, MODE_, UNITS_)                                                                               \
-  rllm_launch_pdl(mlstm_scan_kernel<T_, MODE_>, dim3((dv + 31) / 32, heads, UNITS_), dim3(32 * W), smem, stream, \
+  if (smem > 48 * 1024)                                                                                        \
+    cudaFuncSetAttribute(mlstm_scan_kernel<T_, MODE_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+  rllm_launch_pdl(mlstm_scan_kernel<T_, MODE_>, dim3((dv + ML_COLS - 1) / ML_COLS, heads, UNITS_), dim3(32 * W), smem, stream, \
                   (const T_*)q, (const T_*)k, (const T_*)v, stride, (const float*)gates, qscale, state, q_start,  \
                   slots, out, num_seqs, heads, d, dv, num_slots, local, start, err)
   if (chunks == 0) {

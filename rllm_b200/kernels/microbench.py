@@ -9,6 +9,7 @@
     python -m rllm_b200.kernels.microbench routed_experts --rows 2048 --experts 32 --top 4 --intermediate 1024
     python -m rllm_b200.kernels.microbench lightning_scan --tokens 2048 --heads 16 --head-dim 128 --v-dim 128
     python -m rllm_b200.kernels.microbench selective_scan --tokens 2048 --channels 4096 --state 16
+    python -m rllm_b200.kernels.microbench mlstm_scan --tokens 2048 --heads 8 --head-dim 128 --v-dim 256
     python -m rllm_b200.kernels.microbench streams --tokens 2048 --hidden 2048 --streams 4
 
 Sizes default to the Llama-3.2-1B shape (32 heads, 8 kv heads, head 64, hidden
@@ -77,6 +78,8 @@ def _mask_options(args, rows: int, nq: int, d: int):
         kw["softcap"] = args.softcap
     if args.sinks:
         kw["sinks"] = torch.randn(nq, device=DEV)
+    if args.slopes:
+        kw["slopes"] = torch.tensor([2.0 ** (-args.slopes * (h + 1) / nq) for h in range(nq)], device=DEV)
     if args.gate:
         kw["gate"] = torch.randn(rows, nq if args.gate == "head" else nq * d, device=DEV).bfloat16()
         kw["gate_per_head"] = args.gate == "head"
@@ -277,6 +280,29 @@ def lightning_scan(args) -> None:
           f"of rows and state, {4.0 * T * heads * d * dv / us / 1e6:.2f} TFLOP/s float32")
 
 
+def mlstm_scan(args) -> None:
+    """The matrix memory's recurrence over one prompt portion, or one token of ``--batch`` sequences."""
+    heads, d, dv = args.heads, args.head_dim, args.v_dim or args.head_dim
+    q_start, _, slots, S, per = _one_sequence(args.tokens, args.batch)
+    T, qk = S * per, heads * d
+    bufs = [torch.randn(T, 2 * qk + 2 * heads * dv, device=DEV).bfloat16() for _ in range(4)]
+    pre = torch.randn(T, 2 * heads, device=DEV) * 2
+    gates = torch.empty_like(pre)
+    bias = torch.zeros(heads, device=DEV)
+    state = torch.zeros(S, heads, ops.mlstm_state_size(d, dv), device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+
+    def run(i):
+        a = bufs[i % 4]
+        gates.copy_(pre)                 # (the call turns the pre-activations into log gates in place)
+        ops.mlstm_scan(a[:, :qk], a[:, qk:2 * qk], a[:, 2 * qk:2 * qk + heads * dv], gates, bias, bias, 15.0, d ** -0.5,
+                       state, q_start, slots, S, heads, d, dv, err, q_lens=[per] * S)
+    us = time_us(run, args.iters)
+    moved = T * heads * (4 * d + 6 * dv) + 8 * S * heads * d * dv
+    print(f"mlstm_scan tokens {T} ({S} sequences) heads {heads} x {d} x {dv}: {us:.1f} us (with a copy of the gates), "
+          f"{moved / us / 1e3:.0f} GB/s of rows and state, {4.0 * T * heads * d * dv / us / 1e6:.2f} TFLOP/s float32")
+
+
 def selective_scan(args) -> None:
     """The convolution and the selective recurrence over one prompt portion, or one token of ``--batch`` sequences."""
     E, N, R = args.channels, args.state, max(1, args.channels // 32)
@@ -323,7 +349,7 @@ def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="python -m rllm_b200.kernels.microbench", description=__doc__.split("\n\n")[0])
     p.add_argument("kernel", choices=["attention_decode", "attention_prefill", "gemm_small_m", "gemm_tcgen05",
                                       "latent_attention", "routed_experts", "lightning_scan", "selective_scan",
-                                      "streams"])
+                                      "streams", "mlstm_scan"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=4096)
     p.add_argument("--tokens", type=int, default=2048)
@@ -342,6 +368,8 @@ def main(argv=None) -> int:
     p.add_argument("--chunk", type=int, default=0, help="attention_*: a query sees the keys of its own chunk")
     p.add_argument("--softcap", type=float, default=0.0, help="attention_*: the tanh cap of the scaled scores")
     p.add_argument("--sinks", action="store_true", help="attention_*: one more term a head in the denominator")
+    p.add_argument("--slopes", type=float, default=0.0,
+                   help="attention_*: a distance bias with the slopes 2^(-x (h + 1) / heads) (0: none)")
     p.add_argument("--gate", choices=["head", "element"], default=None, help="attention_*: a sigmoid gate on the result")
     p.add_argument("--v-dim", type=int, default=0, help="lightning_scan: a value head's size (0: --head-dim)")
     p.add_argument("--channels", type=int, default=4096, help="selective_scan: inner channels")
@@ -362,7 +390,7 @@ def main(argv=None) -> int:
     {"attention_decode": attention_decode, "attention_prefill": attention_prefill,
      "gemm_small_m": gemm_small_m, "gemm_tcgen05": gemm_tcgen05, "latent_attention": latent_attention,
      "routed_experts": routed_experts, "lightning_scan": lightning_scan, "selective_scan": selective_scan,
-     "streams": streams}[args.kernel](args)
+     "streams": streams, "mlstm_scan": mlstm_scan}[args.kernel](args)
     return 0
 
 
