@@ -483,15 +483,15 @@ def tibelix(layers, width, mheads, mdim, mvdim, heads, kv_heads, dim, lheads, ld
     moe = {"kind": "moe", "expert": {"ff": ff}, "shared": {"ff": shared},
            "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}}}
     att = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
-           "q_temp": {"coef": 0.5, "every": 64}}
+           "q_temp": {"coef": 0.4, "every": 128}}
     lat = {"heads": lheads, "dim": ldim, "rot_dim": lrot, "vdim": lvdim, "q_rank": q_rank, "kv_rank": kv_rank,
            "scale": (ldim + lrot) ** -0.5,
-           "rot": {"base": 250000.0, "dims": lrot, "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+           "rot": {"base": 500000.0, "dims": lrot, "scaling": {"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0}}}
     out = []
     for i in range(layers):
         k = i % 4
         if k == 0:
-            out.append({"type": "mlstm", "mixer": {"heads": mheads, "dim": mdim, "vdim": mvdim, "gate_cap": 15.0},
+            out.append({"type": "mlstm", "mixer": {"heads": mheads, "dim": mdim, "vdim": mvdim, "gate_cap": 12.0},
                         "mlp": {"kind": "dense", "ff": dense}})
         elif k == 2:
             out.append({"type": "latent_attention", "mixer": lat, "mlp": moe})

@@ -295,7 +295,7 @@ def mlstm_scan(args) -> None:
     def run(i):
         a = bufs[i % 4]
         gates.copy_(pre)                 # (the call turns the pre-activations into log gates in place)
-        ops.mlstm_scan(a[:, :qk], a[:, qk:2 * qk], a[:, 2 * qk:2 * qk + heads * dv], gates, bias, bias, 15.0, d ** -0.5,
+        ops.mlstm_scan(a[:, :qk], a[:, qk:2 * qk], a[:, 2 * qk:2 * qk + heads * dv], gates, bias, bias, 10.0, d ** -0.5,
                        state, q_start, slots, S, heads, d, dv, err, q_lens=[per] * S)
     us = time_us(run, args.iters)
     moved = T * heads * (4 * d + 6 * dv) + 8 * S * heads * d * dv
