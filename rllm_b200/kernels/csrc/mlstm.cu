@@ -13,10 +13,10 @@
 // Everything but the loads of q, k and v (which may be bfloat16) is float32 arithmetic;
 // the gates' pre-activations zi, zf arrive as float32.
 //
-//   mlstm_scan           one block per (sequence, head, 64 value columns): it walks the
+//   mlstm_scan           one block per (sequence, head, 64 or 128 value columns): it walks the
 //                        sequence's tokens of this step in order with its slice of S in
-//                        registers (a warp 16 rows, a lane two columns; n alike; every block of a
-//                        head carries n, the first writes it back).  Long portions are cut into chunks of 64
+//                        registers (a warp 16 rows, a lane two or four columns; n alike; every block
+//                        of a head carries n, the first writes it back).  Long portions are cut into chunks of 64
 //                        tokens that run side by side: every chunk's end state from zero, then
 //                        the states at the chunks' starts chunk after chunk (an elementwise
 //                        pass), then every chunk's tokens from its start state.  Either way a
@@ -56,19 +56,18 @@ mlstm_gates_kernel(float* gates, const float* bias_i, const float* bias_f, float
   g[heads + h] = ml_logsigmoid(ml_soft_cap(g[heads + h] + (bias_f ? bias_f[h] : 0.f), cap));
 }
 
-// A block: (64 value columns, head, unit); warp w keeps rows w * ML_R .. of its columns of S in registers (a
-// lane two columns, 32 apart) and lanes 0 .. ML_R - 1 of it the same rows of n.  Tokens go in segments of
+// A block: (32 NC value columns, head, unit); warp w keeps rows w * ML_R .. of its columns of S in registers (a
+// lane NC columns, 32 apart) and lanes 0 .. ML_R - 1 of it the same rows of n.  Tokens go in segments of
 // ML_CHUNK: first the segment's factors exp(b + m' - m), exp(a - m) and maxima m are made once for all threads
-// (the gates fetched side by side, the chain over m walked by one thread).  Then four tokens at a time: their
-// weighted keys and scaled queries are staged in shared memory (two buffers, so one barrier a group serves),
-// every thread updates its rows token after token and adds up its parts of S^T q; the warps' parts (and those of
-// n . q) meet in shared memory, and the first warp finishes the group before last while the others work on.  The
-// next group's values are fetched ahead.
-#define ML_COLS 64
+// (the gates fetched side by side, the chain over m walked by one thread) and the segment's keys, queries and
+// values are put into shared memory as float32, all loads in flight together.  Then four tokens at a time: every
+// thread updates its rows token after token and adds up its parts of S^T q; the warps' parts (and those of n . q)
+// meet in shared memory (two buffers, so one barrier a group serves), and the first warp finishes the group
+// before last while the others work on.
 #define ML_G 4                  // tokens between two barriers
-#define ML_PART (ML_COLS + 1)
 
-template <typename T, int MODE>
+// NC: value columns a lane (a block covers 32 NC columns)
+template <typename T, int MODE, int NC>
 __global__ void __launch_bounds__(512)
 mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* gates, float qscale, float* state,
                   const int* q_start, const int* slots, float* out, int num_seqs, int heads, int d, int dv,
@@ -77,12 +76,14 @@ mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* g
   pdl_launch();
   extern __shared__ __align__(16) float sm[];
   __shared__ float g_keep[ML_CHUNK], g_take[ML_CHUNK], g_m[ML_CHUNK];
+  constexpr int ML_COLS = 32 * NC, ML_PART = ML_COLS + 1;
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, W = blockDim.x >> 5;
   const int dpad = W * ML_R;
-  float* ksb = sm;                       // [2][ML_G][dpad]: exp(a - m) k
-  float* qsb = sm + 2 * ML_G * dpad;     // [2][ML_G][dpad]: q * qscale
-  float* part = sm + 4 * ML_G * dpad;    // [2][ML_G][W][65]: the warps' parts of S^T q for 64 columns, and of n . q
-  const int j0 = blockIdx.x * ML_COLS + lane, j1 = j0 + 32;      // this lane's value columns
+  float* kf = sm;                                  // [ML_CHUNK][dpad]: the segment's keys
+  float* qf = kf + ML_CHUNK * dpad;                // [ML_CHUNK][dpad]: its queries
+  float* vf = qf + ML_CHUNK * dpad;                // [ML_CHUNK][64]: its values of this block's columns
+  float* part = vf + ML_CHUNK * ML_COLS;           // [2][ML_G][W][65]: the warps' parts of S^T q for 64 columns, and of n . q
+  const int j0 = blockIdx.x * ML_COLS + lane;                    // this lane's value columns: j0 + 32 c
   const int h = blockIdx.y;
   int s = blockIdx.z, t0, t1;
   const int unit = blockIdx.z;
@@ -115,64 +116,65 @@ mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* g
   // (MODE 2 reads every chunk's start state, the first one's too, from `start`: the slot is written by the
   // sequence's last chunk, which may run at the same time)
   const float* from = MODE == 2 ? start + ((size_t)unit * heads + h) * per_head : st;
-  const bool live0 = j0 < dv, live1 = j1 < dv;
+  bool live[NC];
+#pragma unroll
+  for (int c = 0; c < NC; ++c) live[c] = j0 + 32 * c < dv;
   const int i0 = w * ML_R;
   const int ni = i0 + lane;              // the row of n this lane keeps (lanes below ML_R)
-  float S0[ML_R], S1[ML_R];
+  float S[NC][ML_R];
   float nreg = 0.f, m = -INFINITY, bsum = 0.f;       // m, bsum: the first thread's
 #pragma unroll
-  for (int r = 0; r < ML_R; ++r) {
-    S0[r] = (MODE != 1 && live0 && i0 + r < d) ? from[(size_t)(i0 + r) * dv + j0] : 0.f;
-    S1[r] = (MODE != 1 && live1 && i0 + r < d) ? from[(size_t)(i0 + r) * dv + j1] : 0.f;
-  }
+  for (int c = 0; c < NC; ++c)
+#pragma unroll
+    for (int r = 0; r < ML_R; ++r)
+      S[c][r] = (MODE != 1 && live[c] && i0 + r < d) ? from[(size_t)(i0 + r) * dv + j0 + 32 * c] : 0.f;
   if (MODE != 1) {
     if (lane < ML_R && ni < d) nreg = from[(size_t)d * dv + ni];
     m = from[(size_t)d * dv + d];
   }
-  // Tokens go through in groups of ML_G between two barriers.  Thread tid < dpad stages element tid of the
-  // group's keys, thread dpad + e element e of its queries (the block has exactly 2 dpad threads).
-  const bool stage_q = tid >= dpad;
-  const int se = stage_q ? tid - dpad : tid;
-  float pst[ML_G], pv0[ML_G], pv1[ML_G];
-  auto fetch = [&](int t, int end) {                   // tokens t .. t + ML_G - 1 (those before `end`)
-#pragma unroll
-    for (int x = 0; x < ML_G; ++x) {
-      const bool in = t + x < end;
-      pst[x] = 0.f;
-      if (in && se < d && !(MODE == 1 && stage_q))
-        pst[x] = to_f32((stage_q ? q : k)[(size_t)(t + x) * stride + (size_t)h * d + se]);
-      pv0[x] = (in && live0) ? to_f32(v[(size_t)(t + x) * stride + (size_t)h * dv + j0]) : 0.f;
-      pv1[x] = (in && live1) ? to_f32(v[(size_t)(t + x) * stride + (size_t)h * dv + j1]) : 0.f;
-    }
-  };
   auto finish = [&](int t, int end, int buf, int g0) { // the first warp: the parts of tokens t .. become outputs
     for (int x = 0; x < ML_G && t + x < end; ++x) {
-      float num0 = 0.f, num1 = 0.f, dot = 0.f;
+      float num[NC], dot = 0.f;
+#pragma unroll
+      for (int c = 0; c < NC; ++c) num[c] = 0.f;
       const float* pp = part + (size_t)((buf * ML_G + x) * W) * ML_PART;
       for (int y = 0; y < W; ++y) {
-        num0 += pp[y * ML_PART + lane];
-        num1 += pp[y * ML_PART + 32 + lane];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) num[c] += pp[y * ML_PART + 32 * c + lane];
         dot += pp[y * ML_PART + ML_COLS];
       }
-      const float inv = 1.0f / (fmaxf(fabsf(dot), expf(-g_m[g0 + x])) + 1e-6f);
-      if (live0) out[(size_t)(t + x) * heads * dv + (size_t)h * dv + j0] = num0 * inv;
-      if (live1) out[(size_t)(t + x) * heads * dv + (size_t)h * dv + j1] = num1 * inv;
+      // (the queries' scale is applied here, to both sums)
+      const float inv = qscale / (fmaxf(fabsf(dot * qscale), expf(-g_m[g0 + x])) + 1e-6f);
+#pragma unroll
+      for (int c = 0; c < NC; ++c)
+        if (live[c]) out[(size_t)(t + x) * heads * dv + (size_t)h * dv + j0 + 32 * c] = num[c] * inv;
     }
   };
+  const int cols = min(ML_COLS, dv - blockIdx.x * ML_COLS);
   for (int seg = t0; seg < t1; seg += ML_CHUNK) {
     const int seg_end = min(seg + ML_CHUNK, t1);
-    fetch(seg, seg_end);
-    // the segment's gates side by side, then the chain over the maximum by one thread; places behind the
-    // segment's end get the factors that leave the state as it is
-    for (int x = tid; x < seg_end - seg; x += blockDim.x) {
+    const int count = seg_end - seg;
+    const int padded = (count + ML_G - 1) / ML_G * ML_G;                   // the last group is filled up
+    // the segment's rows into shared memory as float32 (all loads of a segment are in flight together), zeros
+    // behind its end; its gates side by side, then the chain over the maximum by one thread
+    for (int idx = tid; idx < padded * dpad; idx += blockDim.x) {
+      const int x = idx / dpad, e = idx - x * dpad;
+      const bool in = x < count && e < d;
+      kf[idx] = in ? to_f32(k[(size_t)(seg + x) * stride + (size_t)h * d + e]) : 0.f;
+      if (MODE != 1) qf[idx] = in ? to_f32(q[(size_t)(seg + x) * stride + (size_t)h * d + e]) : 0.f;
+    }
+    for (int idx = tid; idx < padded * ML_COLS; idx += blockDim.x) {
+      const int x = idx / ML_COLS, c = idx - x * ML_COLS;
+      vf[idx] = (x < count && c < cols) ? to_f32(v[(size_t)(seg + x) * stride + (size_t)h * dv + blockIdx.x * ML_COLS + c]) : 0.f;
+    }
+    for (int x = tid; x < count; x += blockDim.x) {
       g_keep[x] = gates[(size_t)(seg + x) * 2 * heads + heads + h];         // b
       g_take[x] = gates[(size_t)(seg + x) * 2 * heads + h];                 // a
     }
     __syncthreads();
     if (tid == 0) {
-      const int padded = (seg_end - seg + ML_G - 1) / ML_G * ML_G;         // the last group is filled up
       for (int x = 0; x < padded; ++x) {
-        if (x >= seg_end - seg) { g_keep[x] = 1.f; g_take[x] = 0.f; g_m[x] = m; continue; }
+        if (x >= count) { g_keep[x] = 1.f; g_take[x] = 0.f; g_m[x] = m; continue; }
         const float b = g_keep[x], a = g_take[x];
         const float m_new = fmaxf(b + m, a);
         g_keep[x] = expf(b + m - m_new);
@@ -186,53 +188,52 @@ mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* g
     int grp = 0;
     for (int t = seg; t < seg_end; t += ML_G, ++grp) {
       const int buf = grp & 1, g0 = grp * ML_G;
-      float v0[ML_G], v1[ML_G];
-#pragma unroll
-      for (int x = 0; x < ML_G; ++x) {
-        float* dst = (stage_q ? qsb : ksb) + (size_t)(buf * ML_G + x) * dpad + se;
-        if (!(MODE == 1 && stage_q)) *dst = pst[x] * (stage_q ? qscale : g_take[g0 + x]);
-        v0[x] = pv0[x];
-        v1[x] = pv1[x];
+      if (grp > 0) {
+        __syncthreads();                 // the parts of the group before are in
+        if (MODE != 1 && w == 0) finish(t - ML_G, seg_end, buf ^ 1, g0 - ML_G);
       }
-      if (t + ML_G < seg_end) fetch(t + ML_G, seg_end);
-      __syncthreads();
-      if (MODE != 1 && w == 0 && grp > 0) finish(t - ML_G, seg_end, buf ^ 1, g0 - ML_G);
 #pragma unroll
       for (int x = 0; x < ML_G; ++x) {
-        const float keep = g_keep[g0 + x];
-        const float4* k4 = (const float4*)(ksb + (size_t)(buf * ML_G + x) * dpad + i0);
-        const float4* q4 = (const float4*)(qsb + (size_t)(buf * ML_G + x) * dpad + i0);
-        float a0 = 0.f, a1 = 0.f;
+        const float keep = g_keep[g0 + x], take = g_take[g0 + x];
+        const float4* k4 = (const float4*)(kf + (size_t)(g0 + x) * dpad + i0);
+        const float4* q4 = (const float4*)(qf + (size_t)(g0 + x) * dpad + i0);
+        float vv[NC], acc[NC];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) { vv[c] = take * vf[(g0 + x) * ML_COLS + 32 * c + lane]; acc[c] = 0.f; }
 #pragma unroll
         for (int r4 = 0; r4 < ML_R / 4; ++r4) {
           const float4 kk = k4[r4];
-          S0[4 * r4 + 0] = fmaf(keep, S0[4 * r4 + 0], kk.x * v0[x]);  S1[4 * r4 + 0] = fmaf(keep, S1[4 * r4 + 0], kk.x * v1[x]);
-          S0[4 * r4 + 1] = fmaf(keep, S0[4 * r4 + 1], kk.y * v0[x]);  S1[4 * r4 + 1] = fmaf(keep, S1[4 * r4 + 1], kk.y * v1[x]);
-          S0[4 * r4 + 2] = fmaf(keep, S0[4 * r4 + 2], kk.z * v0[x]);  S1[4 * r4 + 2] = fmaf(keep, S1[4 * r4 + 2], kk.z * v1[x]);
-          S0[4 * r4 + 3] = fmaf(keep, S0[4 * r4 + 3], kk.w * v0[x]);  S1[4 * r4 + 3] = fmaf(keep, S1[4 * r4 + 3], kk.w * v1[x]);
-          if (MODE != 1) {
-            const float4 qq = q4[r4];
-            a0 = fmaf(S0[4 * r4 + 0], qq.x, a0);  a1 = fmaf(S1[4 * r4 + 0], qq.x, a1);
-            a0 = fmaf(S0[4 * r4 + 1], qq.y, a0);  a1 = fmaf(S1[4 * r4 + 1], qq.y, a1);
-            a0 = fmaf(S0[4 * r4 + 2], qq.z, a0);  a1 = fmaf(S1[4 * r4 + 2], qq.z, a1);
-            a0 = fmaf(S0[4 * r4 + 3], qq.w, a0);  a1 = fmaf(S1[4 * r4 + 3], qq.w, a1);
+          float4 qq = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (MODE != 1) qq = q4[r4];
+#pragma unroll
+          for (int c = 0; c < NC; ++c) {
+            S[c][4 * r4 + 0] = fmaf(keep, S[c][4 * r4 + 0], kk.x * vv[c]);
+            S[c][4 * r4 + 1] = fmaf(keep, S[c][4 * r4 + 1], kk.y * vv[c]);
+            S[c][4 * r4 + 2] = fmaf(keep, S[c][4 * r4 + 2], kk.z * vv[c]);
+            S[c][4 * r4 + 3] = fmaf(keep, S[c][4 * r4 + 3], kk.w * vv[c]);
+            if (MODE != 1) {
+              acc[c] = fmaf(S[c][4 * r4 + 0], qq.x, acc[c]);
+              acc[c] = fmaf(S[c][4 * r4 + 1], qq.y, acc[c]);
+              acc[c] = fmaf(S[c][4 * r4 + 2], qq.z, acc[c]);
+              acc[c] = fmaf(S[c][4 * r4 + 3], qq.w, acc[c]);
+            }
           }
         }
         float pd = 0.f;
         if (lane < ML_R) {
-          nreg = fmaf(keep, nreg, ksb[(size_t)(buf * ML_G + x) * dpad + ni]);
-          if (MODE != 1) pd = nreg * qsb[(size_t)(buf * ML_G + x) * dpad + ni];
+          nreg = fmaf(keep, nreg, take * kf[(size_t)(g0 + x) * dpad + ni]);
+          if (MODE != 1) pd = nreg * qf[(size_t)(g0 + x) * dpad + ni];
         }
         if (MODE != 1) {
           pd = warp_sum(pd);
           float* pp = part + (size_t)((buf * ML_G + x) * W + w) * ML_PART;
-          pp[lane] = a0;
-          pp[32 + lane] = a1;
+#pragma unroll
+          for (int c = 0; c < NC; ++c) pp[32 * c + lane] = acc[c];
           if (lane == 0) pp[ML_COLS] = pd;
         }
       }
     }
-    __syncthreads();          // the segment's last parts are in; and everybody is through with its factors
+    __syncthreads();          // the segment's last parts are in; and everybody is through with its rows and factors
     if (MODE != 1 && w == 0) finish(seg + (grp - 1) * ML_G, seg_end, (grp - 1) & 1, (grp - 1) * ML_G);
   }
   float* to = nullptr;
@@ -240,10 +241,10 @@ mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* g
   if (MODE == 1) to = local + ((size_t)unit * heads + h) * (per_head + 1);
   if (to == nullptr) return;
 #pragma unroll
-  for (int r = 0; r < ML_R; ++r) {
-    if (live0 && i0 + r < d) to[(size_t)(i0 + r) * dv + j0] = S0[r];
-    if (live1 && i0 + r < d) to[(size_t)(i0 + r) * dv + j1] = S1[r];
-  }
+  for (int c = 0; c < NC; ++c)
+#pragma unroll
+    for (int r = 0; r < ML_R; ++r)
+      if (live[c] && i0 + r < d) to[(size_t)(i0 + r) * dv + j0 + 32 * c] = S[c][r];
   if (blockIdx.x == 0) {
     if (lane < ML_R && ni < d) to[(size_t)d * dv + ni] = nreg;
     if (tid == 0) {
@@ -303,17 +304,28 @@ RLLM_EXPORT int rllm_mlstm_scan(const void* q, const void* k, const void* v, int
   if (chunks > 0 && (!local || !start)) return RLLM_E_BADARG;
   if (d > ML_MAX_D || heads > 65535 || num_seqs > 65535 || chunks > 65535) return RLLM_E_UNSUPPORTED;
   const int W = (d + ML_R - 1) / ML_R;
-  const size_t smem = ((size_t)4 * ML_G * W * ML_R + 2 * (size_t)ML_G * W * ML_PART) * sizeof(float);
+  // the walk over a sequence's tokens (decoding, short portions) takes two value columns a lane, so that a few
+  // sequences still make many blocks; the chunk passes take four where the head is wide enough
+  const int nc_chunks = dv > 64 ? 4 : 2;
+#define ML_SMEM(NC_) (((size_t)2 * ML_CHUNK * W * ML_R + (size_t)ML_CHUNK * 32 * (NC_) + 2 * (size_t)ML_G * W * (32 * (NC_) + 1)) * sizeof(float))
   const long long ng = (long long)num_tokens * heads;
   rllm_launch_pdl(mlstm_gates_kernel, dim3((unsigned)((ng + 255) / 256)), dim3(256), (size_t)0, stream, gates, bias_i,
                   bias_f, cap, ng, heads);
   RLLM_LAUNCH_CHECK();
+#define ML_GO_NC(T_, MODE_, NC_, UNITS_)                                                                       \
+  do {                                                                                                         \
+    const size_t smem = ML_SMEM(NC_);                                                                          \
+    if (smem > 48 * 1024)                                                                                      \
+      cudaFuncSetAttribute(mlstm_scan_kernel<T_, MODE_, NC_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    rllm_launch_pdl(mlstm_scan_kernel<T_, MODE_, NC_>, dim3((dv + 32 * NC_ - 1) / (32 * NC_), heads, UNITS_),   \
+                    dim3(32 * W), smem, stream, (const T_*)q, (const T_*)k, (const T_*)v, stride,              \
+                    (const float*)gates, qscale, state, q_start, slots, out, num_seqs, heads, d, dv, num_slots, \
+                    local, start, err);                                                                        \
+  } while (0)
 #define ML_GO(T_, MODE_, UNITS_)                                                                               \
-  if (smem > 48 * 1024)                                                                                        \
-    cudaFuncSetAttribute(mlstm_scan_kernel<T_, MODE_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
-  rllm_launch_pdl(mlstm_scan_kernel<T_, MODE_>, dim3((dv + ML_COLS - 1) / ML_COLS, heads, UNITS_), dim3(32 * W), smem, stream, \
-                  (const T_*)q, (const T_*)k, (const T_*)v, stride, (const float*)gates, qscale, state, q_start,  \
-                  slots, out, num_seqs, heads, d, dv, num_slots, local, start, err)
+  do {                                                                                                         \
+    if (MODE_ != 0 && nc_chunks == 4) ML_GO_NC(T_, MODE_, 4, UNITS_); else ML_GO_NC(T_, MODE_, 2, UNITS_);     \
+  } while (0)
   if (chunks == 0) {
     RLLM_DISPATCH_DTYPE(dtype, TT, ML_GO(TT, 0, num_seqs));
   } else {
@@ -326,6 +338,8 @@ RLLM_EXPORT int rllm_mlstm_scan(const void* q, const void* k, const void* v, int
     RLLM_DISPATCH_DTYPE(dtype, TT, ML_GO(TT, 2, chunks));
   }
 #undef ML_GO
+#undef ML_GO_NC
+#undef ML_SMEM
   RLLM_LAUNCH_CHECK();
   return 0;
 }
