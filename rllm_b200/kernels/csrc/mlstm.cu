@@ -58,13 +58,14 @@ mlstm_gates_kernel(float* gates, const float* bias_i, const float* bias_f, float
 
 // A block: (32 NC value columns, head, unit); warp w keeps rows w * ML_R .. of its columns of S in registers (a
 // lane NC columns, 32 apart) and lanes 0 .. ML_R - 1 of it the same rows of n.  Tokens go in segments of
-// ML_CHUNK: first the segment's factors exp(b + m' - m), exp(a - m) and maxima m are made once for all threads
+// ML_SEG: first the segment's factors exp(b + m' - m), exp(a - m) and maxima m are made once for all threads
 // (the gates fetched side by side, the chain over m walked by one thread) and the segment's keys, queries and
 // values are put into shared memory as float32, all loads in flight together.  Then four tokens at a time: every
 // thread updates its rows token after token and adds up its parts of S^T q; the warps' parts (and those of n . q)
 // meet in shared memory (two buffers, so one barrier a group serves), and the first warp finishes the group
 // before last while the others work on.
 #define ML_G 4                  // tokens between two barriers
+#define ML_SEG 32               // tokens whose rows are staged in shared memory at a time
 
 // NC: value columns a lane (a block covers 32 NC columns)
 template <typename T, int MODE, int NC>
@@ -79,10 +80,10 @@ mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* g
   constexpr int ML_COLS = 32 * NC, ML_PART = ML_COLS + 1;
   const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, W = blockDim.x >> 5;
   const int dpad = W * ML_R;
-  float* kf = sm;                                  // [ML_CHUNK][dpad]: the segment's keys
-  float* qf = kf + ML_CHUNK * dpad;                // [ML_CHUNK][dpad]: its queries
-  float* vf = qf + ML_CHUNK * dpad;                // [ML_CHUNK][64]: its values of this block's columns
-  float* part = vf + ML_CHUNK * ML_COLS;           // [2][ML_G][W][65]: the warps' parts of S^T q for 64 columns, and of n . q
+  float* kf = sm;                                  // [ML_SEG][dpad]: the segment's keys
+  float* qf = kf + ML_SEG * dpad;                  // [ML_SEG][dpad]: its queries
+  float* vf = qf + ML_SEG * dpad;                  // [ML_SEG][32 NC]: its values of this block's columns
+  float* part = vf + ML_SEG * ML_COLS;             // [2][ML_G][W][65]: the warps' parts of S^T q for 64 columns, and of n . q
   const int j0 = blockIdx.x * ML_COLS + lane;                    // this lane's value columns: j0 + 32 c
   const int h = blockIdx.y;
   int s = blockIdx.z, t0, t1;
@@ -151,8 +152,8 @@ mlstm_scan_kernel(const T* q, const T* k, const T* v, int stride, const float* g
     }
   };
   const int cols = min(ML_COLS, dv - blockIdx.x * ML_COLS);
-  for (int seg = t0; seg < t1; seg += ML_CHUNK) {
-    const int seg_end = min(seg + ML_CHUNK, t1);
+  for (int seg = t0; seg < t1; seg += ML_SEG) {
+    const int seg_end = min(seg + ML_SEG, t1);
     const int count = seg_end - seg;
     const int padded = (count + ML_G - 1) / ML_G * ML_G;                   // the last group is filled up
     // the segment's rows into shared memory as float32 (all loads of a segment are in flight together), zeros
@@ -306,8 +307,9 @@ RLLM_EXPORT int rllm_mlstm_scan(const void* q, const void* k, const void* v, int
   const int W = (d + ML_R - 1) / ML_R;
   // the walk over a sequence's tokens (decoding, short portions) takes two value columns a lane, so that a few
   // sequences still make many blocks; the chunk passes take four where the head is wide enough
-  const int nc_chunks = dv > 64 ? 4 : 2;
-#define ML_SMEM(NC_) (((size_t)2 * ML_CHUNK * W * ML_R + (size_t)ML_CHUNK * 32 * (NC_) + 2 * (size_t)ML_G * W * (32 * (NC_) + 1)) * sizeof(float))
+  const long long warps4 = (long long)((dv + 127) / 128) * heads * (chunks > 0 ? chunks : num_seqs) * W;
+  const int nc_chunks = (dv > 64 && warps4 >= 148LL * 16) ? 4 : 2;      // (four only while the GPU stays filled)
+#define ML_SMEM(NC_) (((size_t)2 * ML_SEG * W * ML_R + (size_t)ML_SEG * 32 * (NC_) + 2 * (size_t)ML_G * W * (32 * (NC_) + 1)) * sizeof(float))
   const long long ng = (long long)num_tokens * heads;
   rllm_launch_pdl(mlstm_gates_kernel, dim3((unsigned)((ng + 255) / 256)), dim3(256), (size_t)0, stream, gates, bias_i,
                   bias_f, cap, ng, heads);
